@@ -1,0 +1,208 @@
+/*
+ * ns_b200.h -- C ABI of libns_b200.so, the sm_100a implementation of NeuralSharp's CUDA inference hot
+ * path (the products behind Linear, causal attention behind MultiHeadAttention, and the small
+ * operators of one cached decoder step).
+ *
+ * Conventions (they follow the reference's P/Invoke layer, src/NeuralSharp/Backends/Cuda/CudaDriver.cs:
+ * 63-77,86-179, so a C# `LibraryImport` binding reads like CudaDriver.cs):
+ *   - every function returns int: 0 = success, otherwise an NS_ERR_* code; ns_last_error() gives the
+ *     text of the calling thread's last failure ("<call> failed: <name> (<code>)" for CUDA errors);
+ *   - device addresses are uint64_t (the reference's CUdeviceptr, CudaBackend.cs:7-10); handles are
+ *     opaque pointers; out-parameters come last;
+ *   - sizes of raw memory calls are BYTES (the reference counts floats; int8 and bf16 buffers exist
+ *     here);
+ *   - all work is queued on the device object's stream; nothing synchronises unless it says so;
+ *   - matrices are row-major and contiguous unless a leading dimension is passed.
+ * There is no CPU fallback: without a CUDA device every compute entry point fails with NS_ERR_CUDA.
+ */
+#ifndef NS_B200_H
+#define NS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NS_API __attribute__((visibility("default")))
+
+enum {
+    NS_OK = 0,
+    NS_ERR_CUDA = 1,        /* a CUDA runtime/driver call failed (text has the CUDA error name) */
+    NS_ERR_ARGUMENT = 2,    /* bad shape, null pointer, misaligned buffer, unsupported combination */
+    NS_ERR_MEMORY = 3,      /* allocation failed or a stated maximum was exceeded */
+    NS_ERR_KERNEL = 4,      /* a kernel's bounded wait ran out; see ns_device_status */
+    NS_ERR_COMM = 5,        /* NCCL reported an error or is not available */
+    NS_ERR_STATE = 6        /* call not valid now (e.g. allocation during stream capture) */
+};
+
+enum { NS_F32 = 0, NS_BF16 = 1, NS_I8 = 2, NS_I32 = 3 };
+
+/* Epilogue of a product: what happens to each accumulator before it is stored. */
+enum {
+    NS_EPI_NONE = 0,        /* + nothing */
+    NS_EPI_BIAS = 1,        /* + bias[n]                        (Linear.ForwardCore, Layers/Linear.cs:43-47) */
+    NS_EPI_BIAS_GELU = 2,   /* gelu_tanh(. + bias[n])           (Tensor.BiasGelu, Tensor.Decoding.cs:44-51) */
+    NS_EPI_BIAS_RESIDUAL = 3 /* . + bias[n] + residual[m,n]      (x + Linear(...), Layers/Attention.cs:201-205) */
+};
+
+typedef struct ns_device_s* ns_device_t;
+typedef struct ns_graph_s* ns_graph_t;
+typedef struct ns_linear_s* ns_linear_t;
+typedef struct ns_kv_cache_s* ns_kv_cache_t;
+typedef struct ns_comm_s* ns_comm_t;
+
+/* ------------------------------------------------------------------------------------------------
+ * Runtime.  Replaces CudaBackend's constructor and CudaDriver's cuInit, cuDeviceGet, cuCtx.. and cuStream..
+ * imports (Backends/Cuda/CudaBackend.cs:48-100,112-139; CudaDriver.cs:86-120).
+ * ------------------------------------------------------------------------------------------------ */
+NS_API const char* ns_last_error(void);
+NS_API const char* ns_error_name(int code);
+NS_API int ns_version(void);
+NS_API int ns_device_count(int* count);
+/* Opens device `ordinal` with a stream of its own. */
+NS_API int ns_device_open(int ordinal, ns_device_t* dev);
+/* Opens device `ordinal` on a stream the caller owns (cudaStream_t as an integer; 0 = legacy default). */
+NS_API int ns_device_open_on_stream(int ordinal, uint64_t stream, ns_device_t* dev);
+NS_API int ns_device_close(ns_device_t dev);
+/* name: at least 128 bytes.  Backend info of CudaBackend.cs:56-60. */
+NS_API int ns_device_info(ns_device_t dev, char* name, int* sm_count, uint64_t* total_bytes, uint64_t* free_bytes);
+NS_API int ns_device_stream(ns_device_t dev, uint64_t* stream);
+/* Backend.Synchronize (Backends/Backend.cs:219). Also reports a kernel whose bounded wait ran out. */
+NS_API int ns_stream_sync(ns_device_t dev);
+/* Reads and clears the device status word: 0 = no kernel gave up a wait. */
+NS_API int ns_device_status(ns_device_t dev, int* status);
+/* Tuning overrides for experiments: tile width (0, 32, 64, 128, 256) and split-K count (0 = heuristic). */
+NS_API int ns_device_tune(ns_device_t dev, int tile_n, int k_splits);
+
+/* ------------------------------------------------------------------------------------------------
+ * Memory.  Replaces Backend.Allocate/Return/Upload/Download/DownloadRange/Fill/Copy
+ * (Backends/Backend.cs:68-86; CudaBackend.cs:185-301).
+ * ------------------------------------------------------------------------------------------------ */
+NS_API int ns_alloc(ns_device_t dev, uint64_t bytes, int zeroed, uint64_t* ptr);
+NS_API int ns_free(ns_device_t dev, uint64_t ptr);
+NS_API int ns_h2d(ns_device_t dev, uint64_t dst, const void* src, uint64_t bytes);        /* synchronous */
+NS_API int ns_d2h(ns_device_t dev, void* dst, uint64_t src, uint64_t bytes);              /* synchronous */
+NS_API int ns_h2d_async(ns_device_t dev, uint64_t dst, const void* src, uint64_t bytes);  /* src should be pinned */
+NS_API int ns_d2h_async(ns_device_t dev, void* dst, uint64_t src, uint64_t bytes);
+NS_API int ns_d2d_async(ns_device_t dev, uint64_t dst, uint64_t src, uint64_t bytes);
+NS_API int ns_memset32_async(ns_device_t dev, uint64_t dst, uint32_t value, uint64_t count);
+NS_API int ns_host_alloc(uint64_t bytes, void** ptr);   /* pinned host memory */
+NS_API int ns_host_free(void* ptr);
+
+/* ------------------------------------------------------------------------------------------------
+ * CUDA graphs.  Replaces Backend.BeginCapture/EndCapture/AbortCapture/ReplayGraph/DestroyGraph
+ * (Backends/Backend.cs:266-281; CudaBackend.Decoding.cs:43-130; capture mode "relaxed" as
+ * CudaDriver.cs:149).
+ * ------------------------------------------------------------------------------------------------ */
+NS_API int ns_capture_begin(ns_device_t dev);
+NS_API int ns_capture_end(ns_device_t dev, ns_graph_t* graph);
+NS_API int ns_capture_abort(ns_device_t dev);
+NS_API int ns_graph_launch(ns_device_t dev, ns_graph_t graph);
+NS_API int ns_graph_destroy(ns_graph_t graph);
+
+/* ------------------------------------------------------------------------------------------------
+ * Products on the tensor cores.  These replace the hot uses of Backend.BatchedMatMul
+ * (Backends/Backend.cs:121-129 -> CudaBackend.BatchedMatMul, CudaBackend.cs:390-408 -> matmul_f32,
+ * PtxKernels.cs:484-627) together with the bias / bias+GELU / residual kernels that follow it
+ * (add_rowvec_f32 PtxKernels.cs:225-234, bias_gelu_f32 PtxKernels.Decoding.cs:93-114, add_f32).
+ * ------------------------------------------------------------------------------------------------ */
+
+/* Row-wise symmetric int8 quantisation: scale[r] = absmax/127 (1 when the row is zero),
+ * q = clamp(rint(x/scale), -127, 127).  x is [rows, cols] of in_dtype (NS_F32 or NS_BF16). */
+NS_API int ns_quantize_rows_i8(ns_device_t dev, uint64_t x, int in_dtype, int64_t rows, int cols, uint64_t q, uint64_t scale);
+
+/* int8 x int8 -> int32 product with the dequantising epilogue fused:
+ *   y[m,n] = epi( ((float)sum_k aq[m,k]*wq[n,k]) * a_scale[m] * w_scale[n] )   (each step rounded to float)
+ * aq [M,K] int8, wq [N,K] int8 (one row per output channel), a_scale [M], w_scale [N], bias [N] or 0,
+ * residual [M,N] of residual_dtype or 0, y [M,N] of out_dtype (NS_F32 or NS_BF16).
+ * raw_s32: when non-zero, the exact int32 accumulators [M,N] are stored there as well.
+ * K must be a multiple of 16. */
+NS_API int ns_qmatmul_i8(ns_device_t dev, uint64_t aq, uint64_t a_scale, uint64_t wq, uint64_t w_scale, uint64_t bias,
+                         uint64_t residual, int residual_dtype, int M, int N, int K, int epilogue, int out_dtype,
+                         uint64_t y, uint64_t raw_s32);
+
+/* bf16 product with float accumulation: C[b] = A[b] * op(B[b]); A [m,k] bf16; B [k,n] bf16 (transB = 0)
+ * or [n,k] (transB = 1); C [m,n] of out_dtype.  Batch stride = one full matrix, as in the reference.
+ * bias [n] float or 0 is added per column when epilogue says so.  k and n multiples of 8. */
+NS_API int ns_matmul_bf16(ns_device_t dev, uint64_t a, uint64_t b, uint64_t c, int batch, int m, int n, int k,
+                          int transB, uint64_t bias, uint64_t residual, int residual_dtype, int epilogue, int out_dtype);
+
+/* ------------------------------------------------------------------------------------------------
+ * Row-wise operators of the bf16 / int8 decoder path.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* LayerNorm over the last dimension, float statistics, two passes, biased variance
+ * (Backend.LayerNormFused, Backends/Backend.cs:227; kernel layernorm_fused_f32,
+ * PtxKernels.Decoding.cs:61-90).  x [rows, cols] of in_dtype (NS_F32 / NS_BF16); gamma, beta float.
+ * out_dtype NS_F32 / NS_BF16: y = LN(x).  out_dtype NS_I8: LN(x) is rounded to bf16 and quantised per
+ * row as ns_quantize_rows_i8 does (q to y, scales to y_scale [rows]) -- the input of the next int8
+ * product, without a round trip through memory. */
+NS_API int ns_layernorm(ns_device_t dev, uint64_t x, int in_dtype, uint64_t gamma, uint64_t beta, int64_t rows, int cols, float eps,
+                        int out_dtype, uint64_t y, uint64_t y_scale);
+
+/* y[b, i, :] = tok_table[ids[b, i], :] + pos_table[pos + i, :]   (Embedding.ForwardCore, Layers/Embedding.cs:38,
+ * + PositionalEncoding.ForwardCached, Layers/Attention.cs:268-269: two gather_f32 launches and an add there).
+ * ids int32 [batch, steps] on the device; pos_dev: int32 device word holding the position of the first
+ * new token (0 = position 0).  Ids are clamped to the table as the reference's GPU gather does. */
+NS_API int ns_embed_pos(ns_device_t dev, uint64_t ids, uint64_t tok_table, uint64_t pos_table, int table_dtype, uint64_t pos_dev,
+                        int batch, int steps, int dim, int vocab, int max_pos, int out_dtype, uint64_t y);
+
+/* ids[r] = index of the first maximum of x[r, 0..cols)  (Tensor.ArgMax -> argmax_f32, PtxKernels.Advanced.cs:144-152;
+ * "first maximum wins", CpuBackend.Advanced.cs:117-138).  x float, rows row_stride elements apart; ids int32. */
+NS_API int ns_argmax_i32(ns_device_t dev, uint64_t x, int rows, int cols, int64_t row_stride, uint64_t ids);
+
+/* counter[0] += delta on the device (DecodingContext.EndStep's affine_f32 on Position, Layers/Decoding.cs:121-127). */
+NS_API int ns_add_i32(ns_device_t dev, uint64_t counter, int32_t delta);
+
+/* Element-wise float <-> bf16 conversion (round to nearest even). */
+NS_API int ns_convert(ns_device_t dev, uint64_t x, int in_dtype, uint64_t y, int out_dtype, int64_t n);
+
+/* Synthetic inputs generated on the device (benchmarks): y[i] = mean + std * N(0,1) from a counter-based
+ * hash of (seed, i); NS_I8 output is rint() clamped to [-127, 127].  ids: uniform int32 in [0, bound). */
+NS_API int ns_fill_normal(ns_device_t dev, uint64_t y, int dtype, int64_t n, uint32_t seed, float mean, float std);
+NS_API int ns_fill_ids(ns_device_t dev, uint64_t y, int64_t n, uint32_t seed, uint32_t bound);
+
+/* ------------------------------------------------------------------------------------------------
+ * float32 operator surface: the Backend methods one cached decoder step calls, with the reference's
+ * argument lists (Backends/Backend.cs, line of each method in brackets).  Storage handles become
+ * device addresses; every count is in floats, as in the reference.
+ * ------------------------------------------------------------------------------------------------ */
+/* [129] c[b] = op(a[b]) * op(b[b]) + beta * c[b]; each element one fused-multiply-add chain over k. */
+NS_API int ns_f32_batched_matmul(ns_device_t dev, uint64_t a, uint64_t b, uint64_t c, int batch, int m, int n, int k,
+                                 int transA, int transB, float beta);
+/* [224] y[r,:] = softmax(scale * x[r,:] + mask[r % maskRows,:]); mask may be 0. */
+NS_API int ns_f32_scale_mask_softmax(ns_device_t dev, uint64_t x, uint64_t mask, uint64_t y, int rows, int cols, int maskRows, float scale);
+/* [227] */
+NS_API int ns_f32_layernorm_fused(ns_device_t dev, uint64_t x, uint64_t gamma, uint64_t beta, uint64_t y, int rows, int cols, float eps);
+/* [230] y[i] = gelu(x[i] + bias[i % cols]) */
+NS_API int ns_f32_bias_gelu(ns_device_t dev, uint64_t x, uint64_t bias, uint64_t y, int64_t n, int cols);
+/* [107] c[r,j] = a[r,j] + v[j] */
+NS_API int ns_f32_add_row_vector(ns_device_t dev, uint64_t a, uint64_t v, uint64_t c, int rows, int cols);
+/* [95] Binary(Add): c = a + b */
+NS_API int ns_f32_add(ns_device_t dev, uint64_t a, uint64_t b, uint64_t c, int64_t n);
+/* [98] y = alpha * x + beta */
+NS_API int ns_f32_affine(ns_device_t dev, uint64_t x, uint64_t y, int64_t n, float alpha, float beta);
+/* [119] y[i] += scale * s[0] */
+NS_API int ns_f32_add_broadcast_scalar(ns_device_t dev, uint64_t s, uint64_t y, int64_t n, float scale);
+/* [235] mask[i,j] = j <= position + i ? 0 : -1e9; position is a float in device memory */
+NS_API int ns_f32_decoder_mask(ns_device_t dev, uint64_t position, uint64_t mask, int rows, int capacity);
+/* [238] cache[h, position + t, :] = source[h, t, :] */
+NS_API int ns_f32_key_value_write(ns_device_t dev, uint64_t source, uint64_t cache, uint64_t position, int heads, int steps, int capacity, int dim);
+/* [172] y[i,:] = table[indices[i],:]; indices are float-encoded, truncated and clamped (GPU behaviour of the reference) */
+NS_API int ns_f32_gather(ns_device_t dev, uint64_t table, uint64_t indices, uint64_t y, int count, int dim, int vocabulary);
+/* [140] y[r] = (float) index of the first maximum of row r */
+NS_API int ns_f32_argmax(ns_device_t dev, uint64_t x, uint64_t y, int rows, int cols);
+/* same, row r starting at x[r * row_stride + row_offset] (the sampler's rowStride/rowOffset convention, Backend.cs:248) */
+NS_API int ns_f32_argmax_strided(ns_device_t dev, uint64_t x, uint64_t y, int rows, int cols, int64_t row_stride, int64_t row_offset);
+/* [193] y (+)= x permuted; outShape / inStrides have `rank` (<= 6) entries */
+NS_API int ns_f32_permute(ns_device_t dev, uint64_t x, uint64_t y, const int* outShape, const int* inStrides, int rank, int accumulate);
+/* [199] dst[dstOffset + r*dstStride + c] (+)= src[srcOffset + r*srcStride + c] */
+NS_API int ns_f32_copy2d(ns_device_t dev, uint64_t src, int64_t srcOffset, int srcStride, uint64_t dst, int64_t dstOffset, int dstStride,
+                         int rows, int cols, int accumulate);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NS_B200_H */

@@ -1,0 +1,65 @@
+"""bf16 x bf16 -> float product (ns_matmul_bf16) against the oracle: <= 1e-2 relative, |e-a| <= tol*max(1,|e|).
+
+Config: squares {1024, 4096, 8192} and the skinny shape M=8, K=4096, N=14336 (BASELINE config "bf16 dense MatMul",
+seed 2); B is stored [K, N] as in the config (and as Linear.Weight in the reference) and also [N, K].
+"""
+import numpy as np
+import pytest
+
+from nn_b200 import native as N
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _run(dev, a_bits, b_bits, m, n, k, transB, out_dtype=N.NS_BF16, batch=1, bias=None, epilogue=N.EPI_NONE):
+    d_a, d_b = dev.from_numpy(a_bits), dev.from_numpy(b_bits)
+    d_c = dev.empty(batch * m * n, out_dtype)
+    d_bias = dev.from_numpy(bias) if bias is not None else None
+    N.call("ns_matmul_bf16", dev.handle, d_a.ptr, d_b.ptr, d_c.ptr, batch, m, n, k, int(transB), d_bias.ptr if d_bias else 0, 0, 0,
+           epilogue, out_dtype)
+    dev.synchronize()
+    return d_c.download((batch, m, n))
+
+
+@pytest.mark.parametrize("transB", [False, True])
+@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (3, 16, 24), (17, 40, 72), (64, 48, 72), (130, 72, 96), (128, 256, 64), (257, 520, 1032)])
+def test_small_shapes(dev, orc, m, n, k, transB):
+    a = orc.round_bf16(orc.normal((m, k), 21))
+    b = orc.round_bf16(orc.normal((n, k) if transB else (k, n), 22))
+    c = _run(dev, a, b, m, n, k, transB, out_dtype=N.NS_F32)[0]
+    exp = orc.matmul_bf16(a, b, b_is_nk=transB)
+    assert orc.close(exp, c, 1e-4), f"max err {orc.max_err(exp, c)}"   # float output of a short sum: accumulation-order noise only
+    cb = _run(dev, a, b, m, n, k, transB, out_dtype=N.NS_BF16)[0]
+    assert orc.close(orc.widen_bf16(orc.round_bf16(exp)), orc.widen_bf16(cb), TOL)
+
+
+def test_batched_and_bias(dev, orc):
+    batch, m, n, k = 3, 40, 64, 128
+    a = orc.round_bf16(orc.normal((batch, m, k), 23))
+    b = orc.round_bf16(orc.normal((batch, k, n), 24))
+    bias = orc.normal((n,), 25)
+    c = _run(dev, a, b, m, n, k, False, out_dtype=N.NS_F32, batch=batch, bias=bias, epilogue=N.EPI_BIAS)
+    for i in range(batch):
+        exp = orc.matmul_bf16(a[i], b[i], b_is_nk=False) + bias[None, :]
+        assert orc.close(exp, c[i], 1e-4)
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (4096, 4096, 4096), (8192, 8192, 8192), (8, 14336, 4096)])
+def test_baseline_shapes(dev, orc, m, n, k):
+    """Oracle on sampled rows; B stored [K, N] as the config states."""
+    a = orc.round_bf16(orc.normal((m, k), 2))
+    b = orc.round_bf16(orc.normal((k, n), 3))
+    c = _run(dev, a, b, m, n, k, False, out_dtype=N.NS_BF16)[0]
+    rows = sorted(set([0, m - 1, m // 2] + list(np.random.default_rng(7).integers(0, m, 5))))
+    bt = np.ascontiguousarray(b.T)  # [N, K] for the oracle's inner loop
+    for r in rows:
+        exp = orc.matmul_bf16(a[r:r + 1], bt, b_is_nk=True)
+        assert orc.close(orc.widen_bf16(orc.round_bf16(exp)), orc.widen_bf16(c[r:r + 1]), TOL), f"row {r}: {orc.max_err(exp, orc.widen_bf16(c[r:r+1]))}"
+    # linearity property on the full output: (column sums of C) ~= (column sums of A) . B, in float64
+    if m <= 4096:
+        a_sum = orc.widen_bf16(a).astype(np.float64).sum(axis=0)
+        exp_cols = a_sum @ orc.widen_bf16(b).astype(np.float64)
+        got_cols = orc.widen_bf16(c).astype(np.float64).sum(axis=0)
+        # each output is rounded to bf16 (relative 2^-9); the sum of m such roundings stays well inside this bound
+        assert np.all(np.abs(exp_cols - got_cols) <= 2e-3 * np.sqrt(k) * m)

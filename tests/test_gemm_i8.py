@@ -1,0 +1,131 @@
+"""int8 x int8 -> int32 product with the dequantising epilogue (ns_qmatmul_i8) against the oracle.
+
+Accumulators must be bit-exact; the float epilogue is computed in the same operation order as the oracle, so
+it is compared bit-exactly too (tolerance 0) except through GELU, where tanhf differs by ulps (1e-5).
+Config: K = N = 4096, M in {1, 16, 128, 2048, 8192} (BASELINE config "int8 QuantizedMatMul sweep", seed 1).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from nn_b200 import native as N
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(dev, aq, a_scale, wq, w_scale, bias=None, residual=None, epilogue=N.EPI_NONE, out_dtype=N.NS_F32, want_raw=True,
+         residual_dtype=N.NS_F32):
+    M, K = aq.shape
+    Nn = wq.shape[0]
+    d_a, d_w = dev.from_numpy(aq), dev.from_numpy(wq)
+    d_as, d_ws = dev.from_numpy(a_scale), dev.from_numpy(w_scale)
+    d_b = dev.from_numpy(bias) if bias is not None else None
+    d_r = dev.from_numpy(residual) if residual is not None else None
+    d_y = dev.empty(M * Nn, out_dtype)
+    d_raw = dev.empty(M * Nn, N.NS_I32) if want_raw else None
+    N.call("ns_qmatmul_i8", dev.handle, d_a.ptr, d_as.ptr, d_w.ptr, d_ws.ptr, d_b.ptr if d_b else 0, d_r.ptr if d_r else 0,
+           residual_dtype, M, Nn, K, epilogue, out_dtype, d_y.ptr, d_raw.ptr if d_raw else 0)
+    dev.synchronize()
+    y = d_y.download((M, Nn))
+    raw = d_raw.download((M, Nn)) if want_raw else None
+    return y, raw
+
+
+def _inputs(orc, M, Nn, K, seed=1):
+    a = orc.normal((M, K), seed, 1.0)
+    w = orc.normal((Nn, K), seed + 100, 0.02)
+    bias = orc.normal((Nn,), seed + 200, 0.01)
+    aq, a_s = orc.quantize_rows_i8(a)
+    wq, w_s = orc.quantize_rows_i8(w)
+    return aq, a_s, wq, w_s, bias
+
+
+@pytest.mark.parametrize("M,Nn,K", [(1, 64, 16), (3, 40, 48), (17, 33 * 4, 144), (128, 256, 128), (130, 72, 1040),
+                                    (129, 520, 4096), (64, 2048, 8192), (300, 1000, 256)])
+def test_small_shapes_bit_exact(dev, orc, M, Nn, K):
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=11)
+    y, raw = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS)
+    acc = orc.qmatmul_i8_acc(aq, wq)
+    assert np.array_equal(raw, acc), f"accumulators differ at {np.argwhere(raw != acc)[:4]}"
+    exp = orc.dequant_epilogue(acc, a_s, w_s, bias)
+    assert np.array_equal(y.view(np.uint32), exp.view(np.uint32)), f"max err {orc.max_err(exp, y)}"
+
+
+@pytest.mark.parametrize("tile_n,splits", [(64, 1), (128, 1), (256, 1), (64, 4), (128, 3), (256, 2)])
+def test_tilings_and_split_k(dev, orc, tile_n, splits):
+    M, Nn, K = 200, 768, 2048
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=12)
+    dev.tune(tile_n, splits)
+    try:
+        y, raw = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS)
+    finally:
+        dev.tune(0, 0)
+    acc = orc.qmatmul_i8_acc(aq, wq)
+    assert np.array_equal(raw, acc)
+    exp = orc.dequant_epilogue(acc, a_s, w_s, bias)
+    assert np.array_equal(y.view(np.uint32), exp.view(np.uint32))
+
+
+def test_epilogues(dev, orc):
+    M, Nn, K = 96, 512, 512
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=13)
+    acc = orc.qmatmul_i8_acc(aq, wq)
+    res = orc.normal((M, Nn), 77, 1.0)
+    # none
+    y, _ = _run(dev, aq, a_s, wq, w_s, None, epilogue=N.EPI_NONE)
+    assert np.array_equal(y.view(np.uint32), orc.dequant_epilogue(acc, a_s, w_s).view(np.uint32))
+    # bias + gelu (tanhf differs by ulps between libm and CUDA)
+    y, _ = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS_GELU)
+    assert orc.close(orc.dequant_epilogue(acc, a_s, w_s, bias, act=1), y, 1e-5)
+    # bias + residual (float residual)
+    y, _ = _run(dev, aq, a_s, wq, w_s, bias, residual=res, epilogue=N.EPI_BIAS_RESIDUAL)
+    assert np.array_equal(y.view(np.uint32), orc.dequant_epilogue(acc, a_s, w_s, bias, residual=res).view(np.uint32))
+    # bf16 residual and bf16 output
+    res_b = orc.round_bf16(res)
+    y, _ = _run(dev, aq, a_s, wq, w_s, bias, residual=res_b, epilogue=N.EPI_BIAS_RESIDUAL, out_dtype=N.NS_BF16, residual_dtype=N.NS_BF16)
+    exp = orc.round_bf16(orc.dequant_epilogue(acc, a_s, w_s, bias, residual=orc.widen_bf16(res_b)))
+    assert np.array_equal(y, exp)
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 2048, 8192])
+def test_baseline_sweep(dev, orc, M):
+    """K = N = 4096.  Oracle on sampled rows (all rows when M <= 128); exact row/column checksums on everything."""
+    K = Nn = 4096
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=1)
+    y, raw = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS)
+    rows = list(range(M)) if M <= 128 else sorted(set([0, 1, 127, 128, 129, M // 2, M - 129, M - 2, M - 1] +
+                                                      list(np.random.default_rng(5).integers(0, M, 24))))
+    for r in rows:
+        acc = orc.qmatmul_i8_acc(aq, wq, r, 1)
+        assert np.array_equal(raw[r:r + 1], acc), f"row {r}"
+        exp = orc.dequant_epilogue(acc, a_s, w_s, bias, row0=r)
+        assert np.array_equal(y[r:r + 1].view(np.uint32), exp.view(np.uint32)), f"row {r}"
+    # size-independent property: sum_n acc[m, n] == aq[m, :] . sum_n wq[n, :]  and  sum_m acc[m, n] == (sum_m aq[m, :]) . wq[n, :]
+    wsum = wq.astype(np.int64).sum(axis=0)
+    asum = aq.astype(np.int64).sum(axis=0)
+    assert np.array_equal(raw.astype(np.int64).sum(axis=1), aq.astype(np.int64) @ wsum)
+    assert np.array_equal(raw.astype(np.int64).sum(axis=0), wq.astype(np.int64) @ asum)
+
+
+def test_extreme_values(dev, orc):
+    """All operands at +-127: the largest accumulator magnitude K * 127^2 must be exact."""
+    M, Nn, K = 128, 64, 8192
+    aq = np.full((M, K), 127, np.int8)
+    aq[1::2] = -127
+    wq = np.full((Nn, K), -127, np.int8)
+    ones_m, ones_n = np.ones(M, np.float32), np.ones(Nn, np.float32)
+    _, raw = _run(dev, aq, ones_m, wq, ones_n)
+    assert np.array_equal(raw, orc.qmatmul_i8_acc(aq, wq))
+    assert raw.min() == -K * 127 * 127 and raw.max() == K * 127 * 127
+
+
+def test_argument_errors(dev):
+    with pytest.raises(N.NsError):
+        N.call("ns_qmatmul_i8", dev.handle, 0, 0, 0, 0, 0, 0, 0, 4, 4, 16, 0, 0, 0, 0)
+    a = dev.empty(64, N.NS_I8)
+    s = dev.empty(64, N.NS_F32)
+    with pytest.raises(N.NsError):  # K not a multiple of 16
+        N.call("ns_qmatmul_i8", dev.handle, a.ptr, s.ptr, a.ptr, s.ptr, 0, 0, 0, 2, 2, 24, 0, 0, s.ptr, 0)
+    with pytest.raises(N.NsError):  # bias epilogue without a bias
+        N.call("ns_qmatmul_i8", dev.handle, a.ptr, s.ptr, a.ptr, s.ptr, 0, 0, 0, 2, 2, 16, N.EPI_BIAS, 0, s.ptr, 0)

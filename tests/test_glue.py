@@ -1,0 +1,78 @@
+"""Row-wise operators of the bf16 / int8 path against the oracle: quantisation bit-exact, LayerNorm within
+1e-4 (float output) / one bf16 ulp, fused LayerNorm -> int8 against the same composition in the oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from nn_b200 import native as N
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 16), (5, 100), (64, 2048), (33, 8192)])
+def test_quantize_rows_bit_exact(dev, orc, rows, cols):
+    x = orc.normal((rows, cols), 81, 1.5)
+    x[0, :] = 0.0  # all-zero row -> scale 1
+    if rows > 2:
+        x[2, 0] = 1e-30
+    for dtype, host in ((N.NS_F32, x), (N.NS_BF16, orc.round_bf16(x))):
+        dx = dev.from_numpy(host)
+        dq, ds = dev.empty(rows * cols, N.NS_I8), dev.empty(rows)
+        N.call("ns_quantize_rows_i8", dev.handle, dx.ptr, dtype, C.c_int64(rows), cols, dq.ptr, ds.ptr)
+        dev.synchronize()
+        q, s = orc.quantize_rows_i8(host)
+        assert np.array_equal(s, ds.download())
+        assert np.array_equal(q, dq.download((rows, cols)))
+
+
+@pytest.mark.parametrize("rows,cols", [(3, 128), (64, 2048), (7, 8192)])
+def test_layernorm_variants(dev, orc, rows, cols):
+    x = orc.normal((rows, cols), 91, 2.0)
+    g, b = orc.normal((cols,), 92, 0.5, 1.0), orc.normal((cols,), 93, 0.1)
+    exp = orc.layernorm_fused(x, g, b)
+    dg, db = dev.from_numpy(g), dev.from_numpy(b)
+    dx = dev.from_numpy(x)
+    dy = dev.empty(rows * cols)
+    N.call("ns_layernorm", dev.handle, dx.ptr, N.NS_F32, dg.ptr, db.ptr, C.c_int64(rows), cols, C.c_float(1e-5), N.NS_F32, dy.ptr, 0)
+    dev.synchronize()
+    assert orc.close(exp, dy.download((rows, cols)), 1e-4)
+    # bf16 in, int8 out: compare with the oracle composition on the same bf16 input; the statistics are summed in a
+    # different order, so a value on a rounding boundary may move by one step: allow |dq| <= 1 on < 0.1 % of elements
+    xb = orc.round_bf16(x)
+    expb = orc.layernorm_fused(orc.widen_bf16(xb), g, b)
+    q_exp, s_exp = orc.quantize_rows_i8(orc.round_bf16(expb))
+    dxb = dev.from_numpy(xb)
+    dq, ds = dev.empty(rows * cols, N.NS_I8), dev.empty(rows)
+    N.call("ns_layernorm", dev.handle, dxb.ptr, N.NS_BF16, dg.ptr, db.ptr, C.c_int64(rows), cols, C.c_float(1e-5), N.NS_I8, dq.ptr, ds.ptr)
+    dyb = dev.empty(rows * cols, N.NS_BF16)
+    N.call("ns_layernorm", dev.handle, dxb.ptr, N.NS_BF16, dg.ptr, db.ptr, C.c_int64(rows), cols, C.c_float(1e-5), N.NS_BF16, dyb.ptr, 0)
+    dev.synchronize()
+    assert orc.close(s_exp, ds.download(), 1e-2)
+    dq_h = dq.download((rows, cols)).astype(np.int32)
+    diff = np.abs(dq_h - q_exp.astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
+    assert orc.close(expb, orc.widen_bf16(dyb.download((rows, cols))), 1e-2)
+
+
+def test_embed_argmax_counter(dev, orc):
+    V, D, ctx, B, T = 50, 64, 32, 3, 4
+    tok = orc.round_bf16(orc.normal((V, D), 101, 0.02))
+    pos = orc.round_bf16(orc.normal((ctx, D), 102, 0.02))
+    ids = np.array(orc.token_ids((B, T), 103, V), np.int32)
+    dtok, dpos, dids = dev.from_numpy(tok), dev.from_numpy(pos), dev.from_numpy(ids)
+    dp = dev.from_numpy(np.array([5], np.int32))
+    dy = dev.empty(B * T * D, N.NS_BF16)
+    N.call("ns_embed_pos", dev.handle, dids.ptr, dtok.ptr, dpos.ptr, N.NS_BF16, dp.ptr, B, T, D, V, ctx, N.NS_BF16, dy.ptr)
+    N.call("ns_add_i32", dev.handle, dp.ptr, T)
+    dev.synchronize()
+    exp = orc.widen_bf16(tok)[ids] + orc.widen_bf16(pos)[5:5 + T][None]
+    assert np.array_equal(orc.round_bf16(exp), dy.download((B, T, D)))
+    assert dp.download()[0] == 9
+    x = orc.normal((5, 32000), 104)
+    x[1, 31999] = 50.0
+    x[2, [7, 20000]] = 60.0
+    dx, di = dev.from_numpy(x), dev.empty(5, N.NS_I32)
+    N.call("ns_argmax_i32", dev.handle, dx.ptr, 5, 32000, C.c_int64(32000), di.ptr)
+    dev.synchronize()
+    assert np.array_equal(orc.argmax(x).astype(np.int32), di.download())
