@@ -102,6 +102,12 @@ NS_API int ns_capture_abort(ns_device_t dev);
 NS_API int ns_graph_launch(ns_device_t dev, ns_graph_t graph);
 NS_API int ns_graph_destroy(ns_graph_t graph);
 
+/* Events on the device object's stream, for device-side timing (cuEvent* of the driver API). */
+NS_API int ns_event_create(ns_device_t dev, uint64_t* event);
+NS_API int ns_event_record(ns_device_t dev, uint64_t event);
+NS_API int ns_event_elapsed_ms(ns_device_t dev, uint64_t start, uint64_t stop, float* ms);  /* waits for `stop` */
+NS_API int ns_event_destroy(ns_device_t dev, uint64_t event);
+
 /* ------------------------------------------------------------------------------------------------
  * Products on the tensor cores.  These replace the hot uses of Backend.BatchedMatMul
  * (Backends/Backend.cs:121-129 -> CudaBackend.BatchedMatMul, CudaBackend.cs:390-408 -> matmul_f32,

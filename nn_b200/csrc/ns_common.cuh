@@ -153,6 +153,32 @@ NS_DEVINL void ns_tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
         : "memory");
 }
+// TMA tiled stores, this CTA's shared memory -> global, tracked by the issuing thread's bulk groups.
+// Elements outside the tensor are clipped by the hardware.
+NS_DEVINL void ns_tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+NS_DEVINL void ns_tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+NS_DEVINL void ns_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's bulk groups are still reading shared memory
+template <int N>
+NS_DEVINL void ns_bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+// waits until at most N of this thread's bulk groups are incomplete
+template <int N>
+NS_DEVINL void ns_bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+NS_DEVINL void ns_st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 NS_DEVINL void ns_prefetch_tensormap(const CUtensorMap* map)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -1,0 +1,38 @@
+// Interface of the tensor-core product shared by ns_qmatmul_i8, ns_matmul_bf16 and the Linear objects.
+#pragma once
+
+#include "ns_common.cuh"
+
+enum { NS_KIND_I8 = 0, NS_KIND_BF16 = 1 };
+
+struct NsGemmParams {
+    int M, N, K;        // K in elements
+    int k_blocks;       // ceil(K * elsize / 128)
+    int k_splits;       // >= 1
+    int kb_per_split;   // k-blocks per split
+    int tiles_m, tiles_n;
+    int epilogue;       // NS_EPI_*
+    int out_dtype;      // NS_F32 / NS_BF16
+    int residual_dtype;
+    int vec_cols;       // 1: w_scale and bias are 16-byte aligned (vector loads in the epilogue)
+    int tma_store;      // 1: outputs leave through shared memory and TMA stores; 0: direct stores (odd N)
+    void* out;          // [M, N] or null
+    int32_t* raw;       // optional exact accumulators (int8 kind only)
+    const float* a_scale;
+    const float* w_scale;
+    const float* bias;
+    const void* residual;
+    void* partial;      // [k_splits, M, N] 32-bit words when k_splits > 1
+    int* status;
+    int status_base;    // code = status_base + role
+};
+
+// Fills the shape-derived fields of `p`, builds the tensor maps and launches on d->stream.
+// a: [M, K]; b: [N, K] (b_is_kn = false) or [K, N] (b_is_kn = true, bf16 only).
+// partial_override: when non-null, split-K partial sums go there (it must hold
+// k_splits * M * N 32-bit words) instead of the device object's scratch block.
+int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_kn, int M, int N, int K, NsGemmParams p,
+                void* partial_override = nullptr, size_t partial_override_bytes = 0);
+
+// Tile width / split count the launcher would pick for a shape (also used to size scratch memory).
+void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* tile_n, int* k_splits);

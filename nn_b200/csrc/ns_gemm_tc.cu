@@ -14,51 +14,44 @@
 //               accumulators in tensor memory; tcgen05.commit releases the ring slot / hands the
 //               accumulator to the epilogue
 //   warps 2..5  epilogue: each warp owns the 32 accumulator lanes of its quadrant (warp % 4), reads
-//               them 32 columns at a time with tcgen05.ld, applies scale / bias / GELU / residual
-//               and stores; then hands the accumulator back, so the next tile's MMAs overlap.
+//               them 32 columns at a time with tcgen05.ld, applies scale / bias / GELU / residual,
+//               writes the [32 rows x 128 B] block to shared memory (swizzled, conflict-free) and
+//               one lane sends it to global memory with a TMA store, which writes whole lines and
+//               clips at the matrix edge; then hands the accumulator back, so the next tile's MMAs
+//               overlap.  (Storing straight from registers, one row per thread, cost 31 us per
+//               128 x 256 float tile: 16-byte pieces of 32 different lines per instruction.)
 // Every wait on an mbarrier is bounded (ns_mbar_wait); a wait that runs out stores a code to the
 // device status block, all roles leave their loops, and tensor memory is released before exit.
-#include "ns_common.cuh"
+#include <stdlib.h>
+#include <string.h>
+
+#include "ns_gemm.cuh"
 
 namespace {
 
 constexpr int BM = 128;          // rows of A per tile = accumulator lanes
 constexpr int BKB = 128;         // bytes of K per k-block = one swizzle atom
 constexpr int GEMM_THREADS = 192;
+constexpr uint32_t EPI_BUF_BYTES = 4096;                    // 32 rows x 128 B
+constexpr uint32_t EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;       // 4 warps x 2 buffers
 
-enum { KIND_I8 = 0, KIND_BF16 = 1 };
-
-struct GemmParams {
-    int M, N, K;        // K in elements
-    int k_blocks;       // ceil(K * elsize / 128)
-    int k_splits;       // >= 1
-    int kb_per_split;   // k-blocks per split
-    int tiles_m, tiles_n;
-    int epilogue;       // NS_EPI_*
-    int out_dtype;      // NS_F32 / NS_BF16
-    int residual_dtype;
-    void* out;          // [M, N]
-    int32_t* raw;       // optional exact accumulators (int8 kind only)
-    const float* a_scale;
-    const float* w_scale;
-    const float* bias;
-    const void* residual;
-    void* partial;      // [k_splits, M, N] 32-bit words when k_splits > 1
-    int* status;
-    int status_base;    // code = status_base + role
+struct StoreMaps {
+    CUtensorMap out;   // [M, N] of the output type, box 32 rows x 128 B (f32) or 64 B (bf16)
+    CUtensorMap raw;   // [M, N] int32
+    CUtensorMap part;  // [k_splits, M, N] 32-bit words
 };
 
 template <int BN>
 struct TileCfg {
-    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : (BN == 64 ? 8 : 8));
+    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr uint32_t A_BYTES = BM * BKB;
     static constexpr uint32_t B_BYTES = BN * BKB;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr uint32_t TMEM_COLS = (2 * BN) < 32 ? 32 : 2 * BN;
-    static constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+    static constexpr uint32_t TMEM_COLS = 2 * BN;
+    static constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 256;
 };
 
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int item, int& tm, int& tn, int& split)
+__device__ __forceinline__ void tile_coords(const NsGemmParams& p, int item, int& tm, int& tn, int& split)
 {
     // Items are ordered so that CTAs running at the same time share operands in L2: groups of 16
     // row tiles, rows fastest inside a group; splits of one tile are neighbours.
@@ -73,33 +66,200 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int item, int& 
     tn = r / rows_here;
 }
 
-// value -> final output element
+// accumulator bits -> output value (without the residual)
 template <int KIND>
-__device__ __forceinline__ float finish_value(const GemmParams& p, uint32_t bits, float a_scale, int col, const float* w_scale_bias)
+__device__ __forceinline__ float finish_value(const NsGemmParams& p, uint32_t bits, float a_scale, float w_scale, float bias)
 {
     float v;
-    if (KIND == KIND_I8) {
+    if (KIND == NS_KIND_I8) {
         v = __int2float_rn(static_cast<int32_t>(bits));
         v = __fmul_rn(v, a_scale);
-        v = __fmul_rn(v, __ldg(&p.w_scale[col]));
+        v = __fmul_rn(v, w_scale);
     } else {
         v = __uint_as_float(bits);
     }
-    if (p.epilogue != NS_EPI_NONE) v = __fadd_rn(v, __ldg(&p.bias[col]));
+    if (p.epilogue != NS_EPI_NONE) v = __fadd_rn(v, bias);
     if (p.epilogue == NS_EPI_BIAS_GELU) v = ns_gelu_tanh(v);
-    (void)w_scale_bias;
     return v;
 }
 
-__device__ __forceinline__ float load_residual(const GemmParams& p, size_t idx)
+__device__ __forceinline__ float load_residual(const NsGemmParams& p, size_t idx)
 {
     if (p.residual_dtype == NS_BF16) return ns_bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.residual)[idx]);
     return reinterpret_cast<const float*>(p.residual)[idx];
 }
 
+// Adds residual[row, col0 .. col0+32) to v.  Vector loads when the row pitch allows.
+__device__ __forceinline__ void add_residual32(const NsGemmParams& p, size_t base, int col0, float (&v)[32])
+{
+    const bool full = col0 + 32 <= p.N;
+    if (p.residual_dtype == NS_F32 && full && (p.N & 3) == 0) {
+        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.residual) + base);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float4 r4 = src[j];
+            v[4 * j] = __fadd_rn(v[4 * j], r4.x); v[4 * j + 1] = __fadd_rn(v[4 * j + 1], r4.y);
+            v[4 * j + 2] = __fadd_rn(v[4 * j + 2], r4.z); v[4 * j + 3] = __fadd_rn(v[4 * j + 3], r4.w);
+        }
+    } else if (p.residual_dtype == NS_BF16 && full && (p.N & 7) == 0) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.residual) + base);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint4 r4 = src[j];
+            const uint32_t w[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                v[8 * j + 2 * t] = __fadd_rn(v[8 * j + 2 * t], __uint_as_float(w[t] << 16));
+                v[8 * j + 2 * t + 1] = __fadd_rn(v[8 * j + 2 * t + 1], __uint_as_float(w[t] & 0xFFFF0000u));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_residual(p, base + j));
+    }
+}
+
+// Writes this warp's [32 rows x WORDS*4 bytes] block into a staging buffer with the swizzle the
+// store's tensor map expects (128-byte rows: 16-byte piece q of row r at q ^ (r & 7); 64-byte rows:
+// q ^ ((r >> 1) & 3)), then lane 0 queues the TMA store.  Two buffers alternate; before a buffer is
+// written again the store that last read it must have finished reading (wait_group.read 1).
+template <int WORDS>
+__device__ __forceinline__ void stage_and_store(uint32_t buf, int lane, const uint32_t (&w)[32], const CUtensorMap* map, int x, int y, int z,
+                                                bool three_d)
+{
+    if (lane == 0) ns_bulk_wait_read<1>();
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < WORDS / 4; q++) {
+        const int sw = WORDS == 32 ? (q ^ (lane & 7)) : (q ^ ((lane >> 1) & 3));
+        ns_st_shared_v4(buf + lane * (WORDS * 4) + sw * 16, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+    ns_fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+        if (three_d) ns_tma_store_3d(map, buf, x, y, z);
+        else ns_tma_store_2d(map, buf, x, y);
+        ns_bulk_commit();
+    }
+}
+
+// Per-tile constants of one epilogue warp.
+struct EpiCtx {
+    int lane, row0, row, split;
+    bool row_ok;
+    float a_scale;
+    uint32_t bufs;   // two staging buffers
+    int nbuf;        // stores queued so far (selects the buffer)
+};
+
+// Finishes 32 columns [col0, col0+32) of this thread's row from accumulator words r and sends them out.
+// Column scales and biases are read with 16-byte loads at a warp-uniform address (one L1 access
+// serves the warp); the ragged last chunk of a row and unaligned vectors take the scalar path.
+template <int KIND>
+__device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const StoreMaps& sm, EpiCtx& cx, const uint32_t (&r)[32], int col0)
+{
+    const size_t base = (size_t)cx.row * p.N + col0;
+    if (p.k_splits > 1) {
+        if (p.tma_store) {
+            stage_and_store<32>(cx.bufs + (cx.nbuf & 1) * EPI_BUF_BYTES, cx.lane, r, &sm.part, col0, cx.row0, cx.split, true);
+            cx.nbuf++;
+        } else if (cx.row_ok) {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(p.partial) + (size_t)cx.split * p.M * p.N + base;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < p.N) dst[j] = r[j];
+        }
+        return;
+    }
+    if (KIND == NS_KIND_I8 && p.raw != nullptr) {
+        if (p.tma_store) {
+            stage_and_store<32>(cx.bufs + (cx.nbuf & 1) * EPI_BUF_BYTES, cx.lane, r, &sm.raw, col0, cx.row0, 0, false);
+            cx.nbuf++;
+        } else if (cx.row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < p.N) p.raw[base + j] = (int32_t)r[j];
+        }
+    }
+    if (p.out == nullptr) return;
+
+    float v[32];
+    const bool vec_ok = p.vec_cols && col0 + 32 <= p.N;
+    if (KIND == NS_KIND_I8) {
+        if (vec_ok) {
+            const float4* ws4 = reinterpret_cast<const float4*>(p.w_scale + col0);
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const float4 w4 = __ldg(ws4 + q);
+                v[4 * q] = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)r[4 * q]), cx.a_scale), w4.x);
+                v[4 * q + 1] = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)r[4 * q + 1]), cx.a_scale), w4.y);
+                v[4 * q + 2] = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)r[4 * q + 2]), cx.a_scale), w4.z);
+                v[4 * q + 3] = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)r[4 * q + 3]), cx.a_scale), w4.w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                v[j] = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)r[j]), cx.a_scale), __ldg(&p.w_scale[min(col0 + j, p.N - 1)]));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+    }
+    if (p.epilogue != NS_EPI_NONE) {
+        if (vec_ok) {
+            const float4* b4 = reinterpret_cast<const float4*>(p.bias + col0);
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const float4 t = __ldg(b4 + q);
+                v[4 * q] = __fadd_rn(v[4 * q], t.x); v[4 * q + 1] = __fadd_rn(v[4 * q + 1], t.y);
+                v[4 * q + 2] = __fadd_rn(v[4 * q + 2], t.z); v[4 * q + 3] = __fadd_rn(v[4 * q + 3], t.w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __fadd_rn(v[j], __ldg(&p.bias[min(col0 + j, p.N - 1)]));
+        }
+        if (p.epilogue == NS_EPI_BIAS_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = ns_gelu_tanh(v[j]);
+        } else if (p.epilogue == NS_EPI_BIAS_RESIDUAL && cx.row_ok) {
+            add_residual32(p, base, col0, v);
+        }
+    }
+    if (p.out_dtype == NS_F32) {
+        if (p.tma_store) {
+            uint32_t w[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) w[j] = __float_as_uint(v[j]);
+            stage_and_store<32>(cx.bufs + (cx.nbuf & 1) * EPI_BUF_BYTES, cx.lane, w, &sm.out, col0, cx.row0, 0, false);
+            cx.nbuf++;
+        } else if (cx.row_ok) {
+            float* dst = reinterpret_cast<float*>(p.out) + base;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < p.N) dst[j] = v[j];
+        }
+    } else {
+        if (p.tma_store) {
+            uint32_t w[32];
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                w[j] = ns_f32_to_bf16_bits(v[2 * j]) | (uint32_t(ns_f32_to_bf16_bits(v[2 * j + 1])) << 16);
+            stage_and_store<16>(cx.bufs + (cx.nbuf & 1) * EPI_BUF_BYTES, cx.lane, w, &sm.out, col0, cx.row0, 0, false);
+            cx.nbuf++;
+        } else if (cx.row_ok) {
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + base;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < p.N) dst[j] = ns_f32_to_bf16_bits(v[j]);
+        }
+    }
+}
+
 template <int KIND, int BN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p)
+ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ StoreMaps sm, const NsGemmParams p)
 {
     using Cfg = TileCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
@@ -108,7 +268,8 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     volatile int* abort_flag = &abort_flag_storage;
 
     const uint32_t smem_base = (ns_smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t epi_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t bar_base = epi_base + EPI_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
@@ -144,7 +305,7 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint32_t tmem_base;
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
-    constexpr int ELEMS_PER_KB = KIND == KIND_I8 ? 128 : 64;
+    constexpr int ELEMS_PER_KB = KIND == NS_KIND_I8 ? 128 : 64;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
@@ -179,7 +340,7 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = KIND == KIND_I8 ? ns_idesc(2, 1, 0, 0, BM, BN) : ns_idesc(1, 1, 0, B_MN ? 1 : 0, BM, BN);
+            constexpr uint32_t idesc = KIND == NS_KIND_I8 ? ns_idesc(2, 1, 0, 0, BM, BN) : ns_idesc(1, 1, 0, B_MN ? 1 : 0, BM, BN);
             const uint64_t desc_k = ns_desc_base(16, 1024);            // K-major: 8-row groups 1024 B apart
             const uint64_t desc_mn = ns_desc_base(64 * 128, 1024);     // MN-major: 64-column blocks 8 KB apart, 8 k-rows 1 KB apart
             int s = 0;
@@ -208,7 +369,7 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         const uint64_t a_desc = ns_desc_at(desc_k, a_addr + kk * 32);
                         const uint64_t b_desc = B_MN ? ns_desc_at(desc_mn, b_addr + kk * (16 * 128)) : ns_desc_at(desc_k, b_addr + kk * 32);
                         const uint32_t accumulate = (kb > kb0 || kk > 0) ? 1u : 0u;
-                        if (KIND == KIND_I8) ns_mma_i8(d_tmem, a_desc, b_desc, idesc, accumulate);
+                        if (KIND == NS_KIND_I8) ns_mma_i8(d_tmem, a_desc, b_desc, idesc, accumulate);
                         else ns_mma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
                     }
                     ns_tc_commit(empty_bar(s));
@@ -220,6 +381,10 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     } else {
         // ---------------------------------------------------------------- epilogue
         const int quad = warp & 3;
+        EpiCtx cx;
+        cx.lane = lane;
+        cx.bufs = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
+        cx.nbuf = 0;
         int local = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, local++) {
@@ -231,79 +396,37 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             ns_tc_fence_after();
-            const int row = tm * BM + quad * 32 + lane;
-            const bool row_ok = row < p.M;
-            const float a_scale = (KIND == KIND_I8 && row_ok && p.k_splits == 1) ? __ldg(&p.a_scale[row]) : 1.0f;
+            cx.row0 = tm * BM + quad * 32;
+            cx.row = cx.row0 + lane;
+            cx.row_ok = cx.row < p.M;
+            cx.split = split;
+            cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok && p.k_splits == 1) ? __ldg(&p.a_scale[cx.row]) : 1.0f;
             const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
+            const bool warp_has_rows = cx.row0 < p.M;
+            // Two register sets: the tensor-memory load of the next 32 columns is in flight while
+            // the current 32 are finished (tcgen05.ld has a latency of several hundred cycles).
+            uint32_t ra[32], rb[32];
+            __syncwarp();
+            ns_tmem_ld32(t_row, ra);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                uint32_t r[32];
-                __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the divergent stores below
-                ns_tmem_ld32(t_row + c * 32, r);
+            for (int c = 0; c < BN / 32; c += 2) {
                 ns_tc_wait_ld();
-                const int col0 = tn * BN + c * 32;
-                if (!row_ok || col0 >= p.N) continue;
-                const bool full = col0 + 32 <= p.N;
-                const size_t base = (size_t)row * p.N + col0;
-                if (p.k_splits > 1) {
-                    uint32_t* dst = reinterpret_cast<uint32_t*>(p.partial) + (size_t)split * p.M * p.N + base;
-                    if (full && (p.N & 3) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = r[j];
-                    }
-                    continue;
-                }
-                if (KIND == KIND_I8 && p.raw != nullptr) {
-                    if (full && (p.N & 3) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(p.raw + base + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; j++) p.raw[base + j] = (int32_t)r[j];
-                    }
-                }
-                if (p.out == nullptr) continue;
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    int col = min(col0 + j, p.N - 1);
-                    v[j] = finish_value<KIND>(p, r[j], a_scale, col, nullptr);
-                }
-                if (p.epilogue == NS_EPI_BIAS_RESIDUAL) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_residual(p, base + j));
-                }
-                if (p.out_dtype == NS_F32) {
-                    float* dst = reinterpret_cast<float*>(p.out) + base;
-                    if (full && (p.N & 3) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = v[j];
-                    }
-                } else {
-                    uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + base;
-                    if (full && (p.N & 7) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 pk;
-                            pk.x = ns_f32_to_bf16_bits(v[j]) | (uint32_t(ns_f32_to_bf16_bits(v[j + 1])) << 16);
-                            pk.y = ns_f32_to_bf16_bits(v[j + 2]) | (uint32_t(ns_f32_to_bf16_bits(v[j + 3])) << 16);
-                            pk.z = ns_f32_to_bf16_bits(v[j + 4]) | (uint32_t(ns_f32_to_bf16_bits(v[j + 5])) << 16);
-                            pk.w = ns_f32_to_bf16_bits(v[j + 6]) | (uint32_t(ns_f32_to_bf16_bits(v[j + 7])) << 16);
-                            *reinterpret_cast<uint4*>(dst + j) = pk;
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = ns_f32_to_bf16_bits(v[j]);
-                    }
-                }
+                __syncwarp();
+                ns_tmem_ld32(t_row + (c + 1) * 32, rb);
+                if (warp_has_rows && tn * BN + c * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, ra, tn * BN + c * 32);
+                ns_tc_wait_ld();
+                __syncwarp();
+                if (c + 2 < BN / 32) ns_tmem_ld32(t_row + (c + 2) * 32, ra);
+                if (warp_has_rows && tn * BN + (c + 1) * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, rb, tn * BN + (c + 1) * 32);
             }
             ns_tc_fence_before();
             __syncwarp();
             if (lane == 0) ns_mbar_arrive(tempty_bar(acc));
         }
+        // shared memory must stay valid until every queued store has read it, and the kernel's
+        // writes must be complete when it ends
+        if (lane == 0) ns_bulk_wait<0>();
+        __syncwarp();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -323,28 +446,48 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 // Sums split-K partials in split order and applies the epilogue.  One thread per 4 columns.
 template <int KIND>
-__global__ void ns_gemm_splitk_finish_kernel(const GemmParams p)
+__global__ void ns_gemm_splitk_finish_kernel(const NsGemmParams p)
 {
-    const int64_t quads = (int64_t)p.M * ((p.N + 3) / 4);
+    const int qpr = (p.N + 3) / 4;
+    const int64_t quads = (int64_t)p.M * qpr;
+    const bool vec = (p.N & 3) == 0;
     for (int64_t q = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; q < quads; q += (int64_t)gridDim.x * blockDim.x) {
-        const int row = (int)(q / ((p.N + 3) / 4));
-        const int col0 = (int)(q % ((p.N + 3) / 4)) * 4;
-        const float a_scale = KIND == KIND_I8 ? __ldg(&p.a_scale[row]) : 1.0f;
-        for (int j = 0; j < 4 && col0 + j < p.N; j++) {
-            const size_t idx = (size_t)row * p.N + col0 + j;
-            uint32_t bits;
-            if (KIND == KIND_I8) {
-                int32_t s = 0;
-                for (int sp = 0; sp < p.k_splits; sp++) s += reinterpret_cast<const int32_t*>(p.partial)[(size_t)sp * p.M * p.N + idx];
-                bits = (uint32_t)s;
-                if (p.raw != nullptr) p.raw[idx] = s;
-            } else {
-                float s = 0.0f;
-                for (int sp = 0; sp < p.k_splits; sp++) s = __fadd_rn(s, reinterpret_cast<const float*>(p.partial)[(size_t)sp * p.M * p.N + idx]);
-                bits = __float_as_uint(s);
+        const int row = (int)(q / qpr);
+        const int col0 = (int)(q % qpr) * 4;
+        const float a_scale = KIND == NS_KIND_I8 ? __ldg(&p.a_scale[row]) : 1.0f;
+        const size_t idx0 = (size_t)row * p.N + col0;
+        uint32_t bits[4];
+        if (KIND == NS_KIND_I8) {
+            int32_t s[4] = {0, 0, 0, 0};
+            for (int sp = 0; sp < p.k_splits; sp++) {
+                const int32_t* src = reinterpret_cast<const int32_t*>(p.partial) + (size_t)sp * p.M * p.N + idx0;
+                if (vec) {
+                    int4 t = *reinterpret_cast<const int4*>(src);
+                    s[0] += t.x; s[1] += t.y; s[2] += t.z; s[3] += t.w;
+                } else {
+                    for (int j = 0; j < 4 && col0 + j < p.N; j++) s[j] += src[j];
+                }
             }
+            for (int j = 0; j < 4; j++) bits[j] = (uint32_t)s[j];
+        } else {
+            float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int sp = 0; sp < p.k_splits; sp++) {
+                const float* src = reinterpret_cast<const float*>(p.partial) + (size_t)sp * p.M * p.N + idx0;
+                if (vec) {
+                    float4 t = *reinterpret_cast<const float4*>(src);
+                    s[0] = __fadd_rn(s[0], t.x); s[1] = __fadd_rn(s[1], t.y); s[2] = __fadd_rn(s[2], t.z); s[3] = __fadd_rn(s[3], t.w);
+                } else {
+                    for (int j = 0; j < 4 && col0 + j < p.N; j++) s[j] = __fadd_rn(s[j], src[j]);
+                }
+            }
+            for (int j = 0; j < 4; j++) bits[j] = __float_as_uint(s[j]);
+        }
+        for (int j = 0; j < 4 && col0 + j < p.N; j++) {
+            const size_t idx = idx0 + j;
+            if (KIND == NS_KIND_I8 && p.raw != nullptr) p.raw[idx] = (int32_t)bits[j];
             if (p.out == nullptr) continue;
-            float v = finish_value<KIND>(p, bits, a_scale, col0 + j, nullptr);
+            float v = finish_value<KIND>(p, bits[j], a_scale, KIND == NS_KIND_I8 ? __ldg(&p.w_scale[col0 + j]) : 1.0f,
+                                         p.epilogue != NS_EPI_NONE ? __ldg(&p.bias[col0 + j]) : 0.0f);
             if (p.epilogue == NS_EPI_BIAS_RESIDUAL) v = __fadd_rn(v, load_residual(p, idx));
             if (p.out_dtype == NS_F32) reinterpret_cast<float*>(p.out)[idx] = v;
             else reinterpret_cast<uint16_t*>(p.out)[idx] = ns_f32_to_bf16_bits(v);
@@ -353,7 +496,7 @@ __global__ void ns_gemm_splitk_finish_kernel(const GemmParams p)
 }
 
 template <int KIND, int BN, bool B_MN>
-int launch_gemm(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p)
+int launch_gemm(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p)
 {
     using Cfg = TileCfg<BN>;
     auto kernel = ns_gemm_tc_kernel<KIND, BN, B_MN>;
@@ -364,25 +507,27 @@ int launch_gemm(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, con
     }
     int items = p.tiles_m * p.tiles_n * p.k_splits;
     int grid = items < d->sm_count ? items : d->sm_count;
-    kernel<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, d->stream>>>(tmA, tmB, p);
+    kernel<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, d->stream>>>(tmA, tmB, sm, p);
     NS_CUDA(cudaGetLastError());
     return NS_OK;
 }
 
 template <int KIND, bool B_MN>
-int dispatch_bn(NsDevice* d, int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p)
+int dispatch_bn(NsDevice* d, int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p)
 {
     switch (bn) {
-        case 256: return launch_gemm<KIND, 256, B_MN>(d, tmA, tmB, p);
-        case 128: return launch_gemm<KIND, 128, B_MN>(d, tmA, tmB, p);
-        case 64: return launch_gemm<KIND, 64, B_MN>(d, tmA, tmB, p);
+        case 256: return launch_gemm<KIND, 256, B_MN>(d, tmA, tmB, sm, p);
+        case 128: return launch_gemm<KIND, 128, B_MN>(d, tmA, tmB, sm, p);
+        case 64: return launch_gemm<KIND, 64, B_MN>(d, tmA, tmB, sm, p);
         default: return ns_fail(NS_ERR_ARGUMENT, "unsupported tile width %d", bn);
     }
 }
 
+}  // namespace
+
 // Tile width and split count: fill the SMs first (wide tiles when there are enough of them), then
 // split K while every split still has at least 4 k-blocks.
-void choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* bn_out, int* splits_out)
+void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* bn_out, int* splits_out)
 {
     const int tiles_m = (M + BM - 1) / BM;
     int bn = 256;
@@ -409,65 +554,108 @@ void choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* bn_out, i
     *splits_out = splits;
 }
 
-}  // namespace
-
-// Shared by ns_qmatmul_i8, ns_matmul_bf16 and the Linear objects.
-int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_kn, int M, int N, int K, GemmParams p)
+int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_kn, int M, int N, int K, NsGemmParams p,
+                void* partial_override, size_t partial_override_bytes)
 {
-    const int elsize = kind == KIND_I8 ? 1 : 2;
+    const int elsize = kind == NS_KIND_I8 ? 1 : 2;
     NS_REQUIRE(M > 0 && N > 0 && K > 0, NS_ERR_ARGUMENT, "product with an empty dimension (M=%d N=%d K=%d)", M, N, K);
     NS_REQUIRE(((int64_t)K * elsize) % 16 == 0, NS_ERR_ARGUMENT, "K=%d: a row of %d bytes is not a multiple of 16 bytes", K, K * elsize);
-    NS_REQUIRE(!(b_is_kn && kind == KIND_I8), NS_ERR_ARGUMENT, "int8 weights must be stored [N,K]");
+    NS_REQUIRE(!(b_is_kn && kind == NS_KIND_I8), NS_ERR_ARGUMENT, "int8 weights must be stored [N,K]");
     NS_REQUIRE(!b_is_kn || (N % 8) == 0, NS_ERR_ARGUMENT, "N=%d must be a multiple of 8 when B is stored [K,N]", N);
     p.M = M; p.N = N; p.K = K;
     p.k_blocks = (int)(((int64_t)K * elsize + BKB - 1) / BKB);
     int bn, splits;
-    choose_tiling(d, M, N, p.k_blocks, &bn, &splits);
+    ns_gemm_choose_tiling(d, M, N, p.k_blocks, &bn, &splits);
     p.kb_per_split = (p.k_blocks + splits - 1) / splits;
     p.k_splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
     p.tiles_m = (M + BM - 1) / BM;
     p.tiles_n = (N + bn - 1) / bn;
     p.status = d->status_dev;
-    p.status_base = kind == KIND_I8 ? 100 : 200;
+    p.status_base = kind == NS_KIND_I8 ? 100 : 200;
     p.partial = nullptr;
     if (p.k_splits > 1) {
-        int rc = ns_scratch_reserve(d, (size_t)p.k_splits * M * N * 4, &p.partial);
-        if (rc != NS_OK) return rc;
+        const size_t need = (size_t)p.k_splits * M * N * 4;
+        if (partial_override != nullptr) {
+            NS_REQUIRE(need <= partial_override_bytes, NS_ERR_MEMORY, "split-K partial sums need %zu bytes, the fixed scratch block holds %zu",
+                       need, partial_override_bytes);
+            p.partial = partial_override;
+        } else {
+            int rc = ns_scratch_reserve(d, need, &p.partial);
+            if (rc != NS_OK) return rc;
+        }
     }
     CUtensorMap tmA, tmB;
-    const CUtensorMapDataType dt = kind == KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    StoreMaps sm;
+    memset(&sm, 0, sizeof(sm));
+    const CUtensorMapDataType dt = kind == NS_KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const uint32_t box_k = BKB / elsize;
+    int rc;
     {
         uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
         uint64_t strides[1] = {(uint64_t)K * elsize};
         uint32_t box[2] = {box_k, (uint32_t)BM};
-        int rc = ns_make_tensor_map(&tmA, dt, 2, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = ns_make_tensor_map(&tmA, dt, 2, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != NS_OK) return rc;
     }
     if (!b_is_kn) {
         uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
         uint64_t strides[1] = {(uint64_t)K * elsize};
         uint32_t box[2] = {box_k, (uint32_t)bn};
-        int rc = ns_make_tensor_map(&tmB, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = ns_make_tensor_map(&tmB, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != NS_OK) return rc;
     } else {
         uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
         uint64_t strides[1] = {(uint64_t)N * elsize};
         uint32_t box[2] = {64, 64};
-        int rc = ns_make_tensor_map(&tmB, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = ns_make_tensor_map(&tmB, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != NS_OK) return rc;
     }
-    int rc;
-    if (kind == KIND_I8) rc = dispatch_bn<KIND_I8, false>(d, bn, tmA, tmB, p);
-    else if (!b_is_kn) rc = dispatch_bn<KIND_BF16, false>(d, bn, tmA, tmB, p);
-    else rc = dispatch_bn<KIND_BF16, true>(d, bn, tmA, tmB, p);
+    // Output maps.  A TMA store needs a 16-byte aligned base and row pitch; otherwise the kernel
+    // falls back to stores from registers.
+    const size_t out_el = p.out_dtype == NS_F32 ? 4 : 2;
+    bool tma_ok = (N * 4) % 16 == 0;
+    if (p.k_splits == 1) {
+        if (p.out != nullptr) tma_ok = tma_ok && ((size_t)N * out_el) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+        if (p.raw != nullptr) tma_ok = tma_ok && (reinterpret_cast<uintptr_t>(p.raw) & 15) == 0;
+    } else {
+        tma_ok = tma_ok && (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0 && ((size_t)M * N * 4) % 16 == 0;
+    }
+    p.tma_store = tma_ok ? 1 : 0;
+    p.vec_cols = ((reinterpret_cast<uintptr_t>(p.w_scale) | reinterpret_cast<uintptr_t>(p.bias)) & 15) == 0 ? 1 : 0;
+    if (tma_ok) {
+        if (p.k_splits > 1) {
+            uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)p.k_splits};
+            uint64_t strides[2] = {(uint64_t)N * 4, (uint64_t)M * N * 4};
+            uint32_t box[3] = {32, 32, 1};
+            rc = ns_make_tensor_map(&sm.part, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p.partial, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc != NS_OK) return rc;
+        } else {
+            uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+            uint32_t box[2] = {32, 32};
+            if (p.out != nullptr) {
+                uint64_t strides[1] = {(uint64_t)N * out_el};
+                rc = p.out_dtype == NS_F32
+                         ? ns_make_tensor_map(&sm.out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p.out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)
+                         : ns_make_tensor_map(&sm.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+                if (rc != NS_OK) return rc;
+            }
+            if (p.raw != nullptr) {
+                uint64_t strides[1] = {(uint64_t)N * 4};
+                rc = ns_make_tensor_map(&sm.raw, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, p.raw, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+                if (rc != NS_OK) return rc;
+            }
+        }
+    }
+    if (kind == NS_KIND_I8) rc = dispatch_bn<NS_KIND_I8, false>(d, bn, tmA, tmB, sm, p);
+    else if (!b_is_kn) rc = dispatch_bn<NS_KIND_BF16, false>(d, bn, tmA, tmB, sm, p);
+    else rc = dispatch_bn<NS_KIND_BF16, true>(d, bn, tmA, tmB, sm, p);
     if (rc != NS_OK) return rc;
     if (p.k_splits > 1) {
         int64_t quads = (int64_t)M * ((N + 3) / 4);
         int64_t blocks = (quads + 255) / 256;
         if (blocks > (int64_t)d->sm_count * 8) blocks = (int64_t)d->sm_count * 8;
-        if (kind == KIND_I8) ns_gemm_splitk_finish_kernel<KIND_I8><<<(unsigned)blocks, 256, 0, d->stream>>>(p);
-        else ns_gemm_splitk_finish_kernel<KIND_BF16><<<(unsigned)blocks, 256, 0, d->stream>>>(p);
+        if (kind == NS_KIND_I8) ns_gemm_splitk_finish_kernel<NS_KIND_I8><<<(unsigned)blocks, 256, 0, d->stream>>>(p);
+        else ns_gemm_splitk_finish_kernel<NS_KIND_BF16><<<(unsigned)blocks, 256, 0, d->stream>>>(p);
         NS_CUDA(cudaGetLastError());
     }
     return NS_OK;
@@ -494,7 +682,7 @@ extern "C" int ns_qmatmul_i8(ns_device_t h, uint64_t aq, uint64_t a_scale, uint6
     NS_REQUIRE(y != 0 || raw_s32 != 0, NS_ERR_ARGUMENT, "ns_qmatmul_i8: no output buffer");
     rc = check_epilogue(epilogue, bias, residual, residual_dtype, out_dtype);
     if (rc != NS_OK) return rc;
-    GemmParams p = {};
+    NsGemmParams p = {};
     p.epilogue = epilogue;
     p.out_dtype = out_dtype;
     p.residual_dtype = residual_dtype;
@@ -504,7 +692,7 @@ extern "C" int ns_qmatmul_i8(ns_device_t h, uint64_t aq, uint64_t a_scale, uint6
     p.w_scale = reinterpret_cast<const float*>(w_scale);
     p.bias = reinterpret_cast<const float*>(bias);
     p.residual = reinterpret_cast<const void*>(residual);
-    return ns_gemm_run(d, KIND_I8, reinterpret_cast<const void*>(aq), reinterpret_cast<const void*>(wq), false, M, N, K, p);
+    return ns_gemm_run(d, NS_KIND_I8, reinterpret_cast<const void*>(aq), reinterpret_cast<const void*>(wq), false, M, N, K, p);
 }
 
 extern "C" int ns_matmul_bf16(ns_device_t h, uint64_t a, uint64_t b, uint64_t c, int batch, int m, int n, int k, int transB,
@@ -520,14 +708,14 @@ extern "C" int ns_matmul_bf16(ns_device_t h, uint64_t a, uint64_t b, uint64_t c,
     const size_t out_el = out_dtype == NS_F32 ? 4 : 2;
     const size_t res_el = residual_dtype == NS_F32 ? 4 : 2;
     for (int bi = 0; bi < batch; bi++) {
-        GemmParams p = {};
+        NsGemmParams p = {};
         p.epilogue = epilogue;
         p.out_dtype = out_dtype;
         p.residual_dtype = residual_dtype;
         p.out = reinterpret_cast<void*>(c + (uint64_t)bi * m * n * out_el);
         p.bias = reinterpret_cast<const float*>(bias);
         p.residual = residual ? reinterpret_cast<const void*>(residual + (uint64_t)bi * m * n * res_el) : nullptr;
-        rc = ns_gemm_run(d, KIND_BF16, reinterpret_cast<const void*>(a + (uint64_t)bi * m * k * 2),
+        rc = ns_gemm_run(d, NS_KIND_BF16, reinterpret_cast<const void*>(a + (uint64_t)bi * m * k * 2),
                          reinterpret_cast<const void*>(b + (uint64_t)bi * k * n * 2), transB == 0, m, n, k, p);
         if (rc != NS_OK) return rc;
     }

@@ -379,6 +379,50 @@ extern "C" int ns_graph_destroy(ns_graph_t gh)
 }
 
 // ------------------------------------------------------------------------------------------------
+// events (device-side timing on the device object's stream)
+// ------------------------------------------------------------------------------------------------
+extern "C" int ns_event_create(ns_device_t h, uint64_t* event)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(event != nullptr, NS_ERR_ARGUMENT, "ns_event_create: out pointer is null");
+    cudaEvent_t e;
+    NS_CUDA(cudaEventCreate(&e));
+    *event = reinterpret_cast<uint64_t>(e);
+    return NS_OK;
+}
+
+extern "C" int ns_event_record(ns_device_t h, uint64_t event)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_CUDA(cudaEventRecord(reinterpret_cast<cudaEvent_t>(event), d->stream));
+    return NS_OK;
+}
+
+extern "C" int ns_event_elapsed_ms(ns_device_t h, uint64_t start, uint64_t stop, float* ms)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(ms != nullptr, NS_ERR_ARGUMENT, "ns_event_elapsed_ms: out pointer is null");
+    NS_CUDA(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(stop)));
+    NS_CUDA(cudaEventElapsedTime(ms, reinterpret_cast<cudaEvent_t>(start), reinterpret_cast<cudaEvent_t>(stop)));
+    return NS_OK;
+}
+
+extern "C" int ns_event_destroy(ns_device_t h, uint64_t event)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    if (event) NS_CUDA(cudaEventDestroy(reinterpret_cast<cudaEvent_t>(event)));
+    return NS_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
 // tensor maps
 // ------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

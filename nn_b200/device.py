@@ -111,6 +111,20 @@ class Device:
             N.call("ns_device_close", self.handle)
             self.handle = None
 
+    # ---- events
+    def event(self) -> int:
+        e = C.c_uint64()
+        N.call("ns_event_create", self.handle, C.byref(e))
+        return e.value
+
+    def record(self, event: int) -> None:
+        N.call("ns_event_record", self.handle, C.c_uint64(event))
+
+    def elapsed_ms(self, start: int, stop: int) -> float:
+        ms = C.c_float()
+        N.call("ns_event_elapsed_ms", self.handle, C.c_uint64(start), C.c_uint64(stop), C.byref(ms))
+        return ms.value
+
     # ---- graphs (Backend.BeginCapture / EndCapture / ReplayGraph, Backends/Backend.cs:266-281)
     def capture_begin(self) -> None:
         N.call("ns_capture_begin", self.handle)

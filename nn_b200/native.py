@@ -45,6 +45,10 @@ SIGNATURES = {
     "ns_capture_abort": [vp],
     "ns_graph_launch": [vp, vp],
     "ns_graph_destroy": [vp],
+    "ns_event_create": [vp, P(u64)],
+    "ns_event_record": [vp, u64],
+    "ns_event_elapsed_ms": [vp, u64, u64, P(f32)],
+    "ns_event_destroy": [vp, u64],
     "ns_quantize_rows_i8": [vp, u64, i32, i64, i32, u64, u64],
     "ns_qmatmul_i8": [vp, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, u64, u64],
     "ns_matmul_bf16": [vp, u64, u64, u64, i32, i32, i32, i32, i32, u64, u64, i32, i32, i32],

@@ -61,5 +61,7 @@ def test_baseline_shapes(dev, orc, m, n, k):
         a_sum = orc.widen_bf16(a).astype(np.float64).sum(axis=0)
         exp_cols = a_sum @ orc.widen_bf16(b).astype(np.float64)
         got_cols = orc.widen_bf16(c).astype(np.float64).sum(axis=0)
-        # each output is rounded to bf16 (relative 2^-9); the sum of m such roundings stays well inside this bound
-        assert np.all(np.abs(exp_cols - got_cols) <= 2e-3 * np.sqrt(k) * m)
+        # each output is rounded to bf16 (relative error <= 2^-9), so a column sum is off by at most 2^-9 * sum |c|;
+        # the float accumulation adds far less.  Bound used: 2^-8 * sum |c| + 1e-3.
+        bound = 2.0 ** -8 * np.abs(orc.widen_bf16(c).astype(np.float64)).sum(axis=0) + 1e-3
+        assert np.all(np.abs(exp_cols - got_cols) <= bound)
