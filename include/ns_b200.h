@@ -208,6 +208,40 @@ NS_API int ns_f32_permute(ns_device_t dev, uint64_t x, uint64_t y, const int* ou
 NS_API int ns_f32_copy2d(ns_device_t dev, uint64_t src, int64_t srcOffset, int srcStride, uint64_t dst, int64_t dstOffset, int dstStride,
                          int rows, int cols, int accumulate);
 
+/* ------------------------------------------------------------------------------------------------
+ * Key/value cache and attention.  Replaces KeyValueCache + Tensor.WriteKeyValues (Layers/Decoding.cs:14-35,
+ * Tensor.Decoding.cs:62-66 -> kv_write_f32, PtxKernels.Decoding.cs:130-143) and the three-kernel attention of
+ * MultiHeadAttention.ForwardCached / ForwardCore (Layers/Attention.cs:46-118: matmul_f32, scale_mask_softmax_f32,
+ * matmul_f32 with the score tensor in memory).  Keys, values, queries and outputs are bf16.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* Two zero-initialised pools (keys, values) of bf16 [num_pages, heads, page_size, head_dim]; head_dim 32, 64 or 128.
+ * A page table (int32 [batch, max_pages], device memory, owned by the caller) maps (sequence, position / page_size)
+ * to a page; the identity table gives the reference's contiguous cache. */
+NS_API int ns_kv_cache_create(ns_device_t dev, int num_pages, int page_size, int heads, int head_dim, ns_kv_cache_t* cache);
+NS_API int ns_kv_cache_destroy(ns_kv_cache_t cache);
+NS_API int ns_kv_cache_pools(ns_kv_cache_t cache, uint64_t* k_pool, uint64_t* v_pool, uint64_t* bytes_each);
+
+/* cache[b, pos + i, h, :] = k/v[(b * steps + i) * src_stride + h * head_dim + :] for i < steps; pos is an int32 in
+ * device memory (pos_dev), so a captured graph stays valid at every position (Layers/Decoding.cs:81-82). */
+NS_API int ns_kv_append(ns_device_t dev, ns_kv_cache_t cache, uint64_t k, uint64_t v, int64_t src_stride, uint64_t page_table,
+                        int max_pages, uint64_t pos_dev, int batch, int steps);
+
+/* o[b, i, h, :] = softmax_j((q[b, i, h, :] . K[b, j, h, :]) * scale) . V[b, j, h, :] over cached positions j <= pos + i.
+ * q element (b, i, h, d) at q[(b * steps + i) * q_stride + h * head_dim + d], o likewise with o_stride.
+ * Uses the device object's scratch block when the work is split along the cache. */
+NS_API int ns_attention_decode(ns_device_t dev, ns_kv_cache_t cache, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride,
+                               uint64_t page_table, int max_pages, uint64_t pos_dev, int batch, int steps, float scale);
+
+/* Attention over a whole sequence (MultiHeadAttention.ForwardCore, Layers/Attention.cs:46-91) without the
+ * [T, T] score tensor: o[b, h, i, :] = softmax_j((q[b,h,i,:] . k[b,h,j,:]) * scale + mask) . v[b,h,j,:], mask = -inf
+ * for j > i when causal.  head_dim must be 128.  Element (b, h, s, d) of each tensor sits at
+ * base[b * strides[0] + h * strides[1] + s * strides[2] + d] (strides in elements, multiples of 8), so both
+ * [batch, heads, seq, 128] buffers and the [batch * seq, 3 * D] output of a fused QKV product can be used in place. */
+NS_API int ns_attention_prefill(ns_device_t dev, uint64_t q, uint64_t k, uint64_t v, uint64_t o, int batch, int heads, int seq, int head_dim,
+                                const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
+                                float scale, int causal);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,405 @@
+// Paged key/value cache and attention for cached decoding (new queries against the cache).
+//
+// Reference path: MultiHeadAttention.ForwardCached (src/NeuralSharp/Layers/Attention.cs:98-118) with
+// KeyValueCache (Layers/Decoding.cs:14-35): kv_write_f32 appends the new keys/values at a device-side
+// position, then matmul_f32 (Q.K^T over the WHOLE capacity), scale_mask_softmax_f32 with a -1e9 mask
+// and matmul_f32 (P.V) run as three kernels with the score tensor in memory.  Here one kernel reads
+// only positions [0, pos + i] (exactly equivalent: exp(-1e9 - max) is 0 in float and unwritten rows
+// are always masked), keeps scores in shared memory and never writes them out.  The work is
+// HBM-bound (every cached key and value is read once per step), so it runs on the CUDA cores with
+// 16-byte loads; there is no contraction large enough for the tensor cores at one query per head.
+//
+// Cache layout: two pools (keys, values) of bf16 [num_pages, heads, page_size, head_dim]; a page table
+// int32 [batch, max_pages] maps (sequence, position / page_size) to a page.  A contiguous cache is the
+// identity table.  One (page, head) slab is page_size * head_dim * 2 bytes of contiguous memory.
+#include <math.h>
+
+#include "ns_common.cuh"
+
+struct NsKvCache {
+    int ordinal;
+    int num_pages, page_size, heads, head_dim;
+    uint16_t* k_pool;
+    uint16_t* v_pool;
+};
+
+namespace {
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_CHUNK = 1024;  // positions per CTA (scores kept in shared memory)
+
+struct DecodeParams {
+    const uint16_t* q;  // element (b, i, h, d) at q[(b * steps + i) * q_stride + h * dh + d]
+    int64_t q_stride;
+    uint16_t* o;
+    int64_t o_stride;
+    const uint16_t* k_pool;
+    const uint16_t* v_pool;
+    const int32_t* page_table;
+    int max_pages, page_size, heads;
+    const int32_t* pos_dev;
+    int batch, steps, splits;
+    float scale;
+    float* partial;  // [rows, splits, 2 + dh] when splits > 1
+};
+
+__device__ __forceinline__ float warp_max_f(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum_f(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8])
+{
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        f[2 * t] = __uint_as_float(w[t] << 16);
+        f[2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
+    }
+}
+
+// One CTA per (batch, head, new position, split).  DH = head_dim; LPT = DH / 8 lanes cover one row.
+template <int DH>
+__global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const DecodeParams p)
+{
+    constexpr int LPT = DH / 8;               // lanes per cached position
+    constexpr int TPW = 32 / LPT;             // positions per warp per load
+    constexpr int GROUPS = DEC_THREADS / LPT; // positions in flight per CTA in the P.V phase
+    __shared__ float s_scores[DEC_CHUNK];
+    __shared__ float s_red[DEC_THREADS / 32];
+    __shared__ float s_acc[GROUPS][DH];
+
+    int idx = blockIdx.x;
+    const int split = idx % p.splits; idx /= p.splits;
+    const int i = idx % p.steps; idx /= p.steps;
+    const int h = idx % p.heads;
+    const int b = idx / p.heads;
+    const int kv_len = p.pos_dev[0] + i + 1;
+    const int per_split = ((kv_len + p.splits - 1) / p.splits + p.page_size - 1) / p.page_size * p.page_size;
+    const int j0 = split * per_split;
+    const int j1 = min(kv_len, j0 + per_split);
+    const int row_id = (b * p.heads + h) * p.steps + i;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPT;  // which 8 dims of the row this lane owns
+
+    float m_run = -INFINITY, l_run = 0.0f;
+    float acc[8];
+#pragma unroll
+    for (int d = 0; d < 8; d++) acc[d] = 0.0f;
+
+    float qf[8];
+    {
+        const uint16_t* qrow = p.q + (size_t)(b * p.steps + i) * p.q_stride + h * DH + sub * 8;
+        unpack8(*reinterpret_cast<const uint4*>(qrow), qf);
+    }
+    const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
+    const size_t slab = (size_t)p.page_size * DH;
+
+    for (int c0 = j0; c0 < j1; c0 += DEC_CHUNK) {
+        const int c1 = min(j1, c0 + DEC_CHUNK);
+        // ---- scores: s_j = (q . k_j) * scale.  Four rows per lane group are loaded before any is reduced, and the
+        // loop bounds are warp-uniform because the reduction shuffles need every lane.
+        constexpr int SCORE_STRIDE = (DEC_THREADS / 32) * TPW;
+        for (int jb = c0 + warp * TPW; jb < c1; jb += 4 * SCORE_STRIDE) {
+            uint4 kv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = jb + u * SCORE_STRIDE + lane / LPT;
+                kv[u] = make_uint4(0, 0, 0, 0);
+                if (j < c1) {
+                    const int page = __ldg(&pt[j / p.page_size]);
+                    const uint16_t* krow = p.k_pool + ((size_t)page * p.heads + h) * slab + (size_t)(j % p.page_size) * DH + sub * 8;
+                    kv[u] = __ldg(reinterpret_cast<const uint4*>(krow));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = jb + u * SCORE_STRIDE + lane / LPT;
+                float kf[8];
+                unpack8(kv[u], kf);
+                float dot = 0.0f;
+#pragma unroll
+                for (int d = 0; d < 8; d++) dot = fmaf(qf[d], kf[d], dot);
+#pragma unroll
+                for (int o = LPT / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                if (sub == 0 && j < c1) s_scores[j - c0] = dot * p.scale;
+            }
+        }
+        __syncthreads();
+        // ---- chunk maximum, rescale of the running state, exponentials
+        float mx = -INFINITY;
+        for (int j = threadIdx.x; j < c1 - c0; j += DEC_THREADS) mx = fmaxf(mx, s_scores[j]);
+        mx = warp_max_f(mx);
+        if (lane == 0) s_red[warp] = mx;
+        __syncthreads();
+        mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+        const float m_new = fmaxf(m_run, mx);
+        const float alpha = m_run == -INFINITY ? 0.0f : expf(m_run - m_new);
+        __syncthreads();
+        float sum = 0.0f;
+        for (int j = threadIdx.x; j < c1 - c0; j += DEC_THREADS) {
+            const float e = expf(s_scores[j] - m_new);
+            s_scores[j] = e;
+            sum += e;
+        }
+        sum = warp_sum_f(sum);
+        if (lane == 0) s_red[warp] = sum;
+        __syncthreads();
+        sum = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+        l_run = l_run * alpha + sum;
+        m_run = m_new;
+#pragma unroll
+        for (int d = 0; d < 8; d++) acc[d] *= alpha;
+        // ---- o += p_j * v_j ; group g of LPT lanes walks positions g, g + GROUPS, ... four loads in flight
+        for (int jb = c0 + threadIdx.x / LPT; jb < c1; jb += 4 * GROUPS) {
+            uint4 vv[4];
+            float pj[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = jb + u * GROUPS;
+                vv[u] = make_uint4(0, 0, 0, 0);
+                pj[u] = 0.0f;
+                if (j < c1) {
+                    const int page = __ldg(&pt[j / p.page_size]);
+                    const uint16_t* vrow = p.v_pool + ((size_t)page * p.heads + h) * slab + (size_t)(j % p.page_size) * DH + sub * 8;
+                    vv[u] = __ldg(reinterpret_cast<const uint4*>(vrow));
+                    pj[u] = s_scores[j - c0];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float vf[8];
+                unpack8(vv[u], vf);
+#pragma unroll
+                for (int d = 0; d < 8; d++) acc[d] = fmaf(pj[u], vf[d], acc[d]);
+            }
+        }
+        __syncthreads();
+    }
+    // ---- reduce the GROUPS partial outputs
+    const int g = threadIdx.x / LPT;
+#pragma unroll
+    for (int d = 0; d < 8; d++) s_acc[g][sub * 8 + d] = acc[d];
+    __syncthreads();
+    for (int d = threadIdx.x; d < DH; d += DEC_THREADS) {
+        float t = 0.0f;
+#pragma unroll 4
+        for (int gg = 0; gg < GROUPS; gg++) t += s_acc[gg][d];
+        if (p.splits == 1) {
+            p.o[(size_t)(b * p.steps + i) * p.o_stride + h * DH + d] = ns_f32_to_bf16_bits(t / l_run);
+        } else {
+            float* dst = p.partial + ((size_t)row_id * p.splits + split) * (2 + DH);
+            dst[2 + d] = t;
+            if (d == 0) { dst[0] = m_run; dst[1] = l_run; }
+        }
+    }
+}
+
+// Merges the per-split (max, sum, unnormalised output) triples of one row.
+template <int DH>
+__global__ void ns_attention_combine_kernel(const DecodeParams p)
+{
+    const int row_id = blockIdx.x;
+    const int i = row_id % p.steps;
+    const int h = (row_id / p.steps) % p.heads;
+    const int b = row_id / (p.steps * p.heads);
+    const float* src = p.partial + (size_t)row_id * p.splits * (2 + DH);
+    float m = -INFINITY;
+    for (int s = 0; s < p.splits; s++) m = fmaxf(m, src[s * (2 + DH)]);
+    float l = 0.0f;
+    for (int s = 0; s < p.splits; s++) {
+        const float ms = src[s * (2 + DH)];
+        if (ms != -INFINITY) l += src[s * (2 + DH) + 1] * expf(ms - m);
+    }
+    for (int d = threadIdx.x; d < DH; d += blockDim.x) {
+        float t = 0.0f;
+        for (int s = 0; s < p.splits; s++) {
+            const float ms = src[s * (2 + DH)];
+            if (ms != -INFINITY) t += src[s * (2 + DH) + 2 + d] * expf(ms - m);
+        }
+        p.o[(size_t)(b * p.steps + i) * p.o_stride + h * DH + d] = ns_f32_to_bf16_bits(t / l);
+    }
+}
+
+// cache[page(b, pos + i), h, (pos + i) % page_size, :] = src[(b, i), h, :]
+__global__ void ns_kv_append_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v, int64_t src_stride, uint16_t* k_pool,
+                                    uint16_t* v_pool, const int32_t* __restrict__ page_table, int max_pages, int page_size, int heads, int dh,
+                                    const int32_t* pos_dev, int batch, int steps)
+{
+    const int pos0 = pos_dev[0];
+    const int vec = dh / 8;
+    const int64_t n = (int64_t)batch * steps * heads * vec;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(e % vec);
+        const int h = (int)((e / vec) % heads);
+        const int64_t tok = e / ((int64_t)vec * heads);
+        const int i = (int)(tok % steps), b = (int)(tok / steps);
+        const int pos = pos0 + i;
+        if (pos / page_size >= max_pages) continue;
+        const int page = page_table[(size_t)b * max_pages + pos / page_size];
+        const size_t dst = (((size_t)page * heads + h) * page_size + pos % page_size) * dh + c * 8;
+        const size_t src = (size_t)tok * src_stride + h * dh + c * 8;
+        *reinterpret_cast<uint4*>(k_pool + dst) = *reinterpret_cast<const uint4*>(k + src);
+        *reinterpret_cast<uint4*>(v_pool + dst) = *reinterpret_cast<const uint4*>(v + src);
+    }
+}
+
+template <int DH>
+int launch_decode(NsDevice* d, const DecodeParams& p)
+{
+    const int rows = p.batch * p.heads * p.steps;
+    ns_attention_decode_kernel<DH><<<rows * p.splits, DEC_THREADS, 0, d->stream>>>(p);
+    NS_CUDA(cudaGetLastError());
+    if (p.splits > 1) {
+        ns_attention_combine_kernel<DH><<<rows, DH < 64 ? 32 : 64, 0, d->stream>>>(p);
+        NS_CUDA(cudaGetLastError());
+    }
+    return NS_OK;
+}
+
+}  // namespace
+
+extern "C" int ns_kv_cache_create(ns_device_t h, int num_pages, int page_size, int heads, int head_dim, ns_kv_cache_t* out)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(out != nullptr, NS_ERR_ARGUMENT, "ns_kv_cache_create: out handle is null");
+    NS_REQUIRE(num_pages > 0 && page_size > 0 && heads > 0, NS_ERR_ARGUMENT, "ns_kv_cache_create: bad shape");
+    NS_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 128, NS_ERR_ARGUMENT, "ns_kv_cache_create: head_dim must be 32, 64 or 128");
+    NS_REQUIRE(!d->capturing, NS_ERR_STATE, "ns_kv_cache_create: not allowed while the stream is being captured");
+    NsKvCache* c = new NsKvCache();
+    c->ordinal = d->ordinal;
+    c->num_pages = num_pages; c->page_size = page_size; c->heads = heads; c->head_dim = head_dim;
+    const size_t bytes = (size_t)num_pages * heads * page_size * head_dim * 2;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->k_pool), bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&c->v_pool), bytes);
+    if (e != cudaSuccess) {
+        if (c->k_pool) cudaFree(c->k_pool);
+        delete c;
+        cudaGetLastError();
+        return ns_fail(NS_ERR_MEMORY, "key/value pools of 2 x %zu bytes: %s (%d)", bytes, cudaGetErrorName(e), (int)e);
+    }
+    // the reference's cache is zero-initialised (Layers/Decoding.cs:19-20)
+    NS_CUDA(cudaMemsetAsync(c->k_pool, 0, bytes, d->stream));
+    NS_CUDA(cudaMemsetAsync(c->v_pool, 0, bytes, d->stream));
+    *out = reinterpret_cast<ns_kv_cache_t>(c);
+    return NS_OK;
+}
+
+extern "C" int ns_kv_cache_destroy(ns_kv_cache_t ch)
+{
+    NsKvCache* c = reinterpret_cast<NsKvCache*>(ch);
+    if (!c) return NS_OK;
+    cudaSetDevice(c->ordinal);
+    cudaFree(c->k_pool);
+    cudaFree(c->v_pool);
+    delete c;
+    return NS_OK;
+}
+
+extern "C" int ns_kv_cache_pools(ns_kv_cache_t ch, uint64_t* k_pool, uint64_t* v_pool, uint64_t* bytes_each)
+{
+    NsKvCache* c = reinterpret_cast<NsKvCache*>(ch);
+    NS_REQUIRE(c != nullptr, NS_ERR_ARGUMENT, "ns_kv_cache_pools: cache is null");
+    if (k_pool) *k_pool = reinterpret_cast<uint64_t>(c->k_pool);
+    if (v_pool) *v_pool = reinterpret_cast<uint64_t>(c->v_pool);
+    if (bytes_each) *bytes_each = (uint64_t)c->num_pages * c->heads * c->page_size * c->head_dim * 2;
+    return NS_OK;
+}
+
+extern "C" int ns_kv_append(ns_device_t h, ns_kv_cache_t ch, uint64_t k, uint64_t v, int64_t src_stride, uint64_t page_table, int max_pages,
+                            uint64_t pos_dev, int batch, int steps)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NsKvCache* c = reinterpret_cast<NsKvCache*>(ch);
+    NS_REQUIRE(c && k && v && page_table && pos_dev, NS_ERR_ARGUMENT, "ns_kv_append: null argument");
+    NS_REQUIRE(batch >= 0 && steps >= 0 && max_pages > 0, NS_ERR_ARGUMENT, "ns_kv_append: bad shape");
+    NS_REQUIRE(src_stride % 8 == 0 && (k & 15) == 0 && (v & 15) == 0, NS_ERR_ARGUMENT, "ns_kv_append: source rows must be 16-byte aligned");
+    const int64_t n = (int64_t)batch * steps * c->heads * (c->head_dim / 8);
+    if (n == 0) return NS_OK;
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > (int64_t)d->sm_count * 16) blocks = (int64_t)d->sm_count * 16;
+    ns_kv_append_kernel<<<(unsigned)blocks, 256, 0, d->stream>>>(reinterpret_cast<const uint16_t*>(k), reinterpret_cast<const uint16_t*>(v), src_stride,
+                                                                c->k_pool, c->v_pool, reinterpret_cast<const int32_t*>(page_table), max_pages,
+                                                                c->page_size, c->heads, c->head_dim, reinterpret_cast<const int32_t*>(pos_dev), batch,
+                                                                steps);
+    NS_CUDA(cudaGetLastError());
+    return NS_OK;
+}
+
+// Scratch bytes ns_attention_decode needs for `rows` = batch * heads * steps query rows split `splits` ways.
+static size_t decode_scratch_bytes(int rows, int splits, int dh) { return (size_t)rows * splits * (2 + dh) * sizeof(float); }
+
+static int choose_splits(const NsDevice* d, int rows, int max_len, int page_size)
+{
+    int splits = 1;
+    const int target = 2 * d->sm_count;
+    if (rows < target) {
+        splits = (target + rows - 1) / rows;
+        int by_len = max_len / 256;
+        if (by_len < 1) by_len = 1;
+        if (splits > by_len) splits = by_len;
+        if (splits > 32) splits = 32;
+    }
+    (void)page_size;
+    return splits < 1 ? 1 : splits;
+}
+
+int ns_attention_decode_impl(NsDevice* d, NsKvCache* c, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride, uint64_t page_table,
+                             int max_pages, uint64_t pos_dev, int batch, int steps, float scale, float* scratch, size_t scratch_bytes,
+                             bool own_scratch)
+{
+    NS_REQUIRE(c && q && o && page_table && pos_dev, NS_ERR_ARGUMENT, "ns_attention_decode: null argument");
+    NS_REQUIRE(batch > 0 && steps > 0 && max_pages > 0, NS_ERR_ARGUMENT, "ns_attention_decode: bad shape");
+    NS_REQUIRE(q_stride % 8 == 0 && (q & 15) == 0, NS_ERR_ARGUMENT, "ns_attention_decode: query rows must be 16-byte aligned");
+    DecodeParams p;
+    p.q = reinterpret_cast<const uint16_t*>(q); p.q_stride = q_stride;
+    p.o = reinterpret_cast<uint16_t*>(o); p.o_stride = o_stride;
+    p.k_pool = c->k_pool; p.v_pool = c->v_pool;
+    p.page_table = reinterpret_cast<const int32_t*>(page_table);
+    p.max_pages = max_pages; p.page_size = c->page_size; p.heads = c->heads;
+    p.pos_dev = reinterpret_cast<const int32_t*>(pos_dev);
+    p.batch = batch; p.steps = steps; p.scale = scale;
+    const int rows = batch * c->heads * steps;
+    // the context length lives on the device; the split count is sized for the longest possible context
+    p.splits = choose_splits(d, rows, max_pages * c->page_size, c->page_size);
+    p.partial = nullptr;
+    if (p.splits > 1) {
+        const size_t need = decode_scratch_bytes(rows, p.splits, c->head_dim);
+        if (own_scratch) {
+            void* s = nullptr;
+            int rc = ns_scratch_reserve(d, need, &s);
+            if (rc != NS_OK) return rc;
+            p.partial = reinterpret_cast<float*>(s);
+        } else {
+            NS_REQUIRE(need <= scratch_bytes, NS_ERR_MEMORY, "attention partials need %zu bytes, the fixed scratch block holds %zu", need, scratch_bytes);
+            p.partial = scratch;
+        }
+    }
+    switch (c->head_dim) {
+        case 32: return launch_decode<32>(d, p);
+        case 64: return launch_decode<64>(d, p);
+        default: return launch_decode<128>(d, p);
+    }
+}
+
+extern "C" int ns_attention_decode(ns_device_t h, ns_kv_cache_t ch, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride,
+                                   uint64_t page_table, int max_pages, uint64_t pos_dev, int batch, int steps, float scale)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    return ns_attention_decode_impl(d, reinterpret_cast<NsKvCache*>(ch), q, q_stride, o, o_stride, page_table, max_pages, pos_dev, batch, steps,
+                                    scale, nullptr, 0, true);
+}

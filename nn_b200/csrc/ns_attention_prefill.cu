@@ -1,0 +1,354 @@
+// Causal attention forward for a whole sequence (prefill), head_dim 128, bf16 in / bf16 out, on the
+// sm_100a tensor cores: S = Q.K^T and O += P.V are tcgen05.mma with accumulators in tensor memory,
+// Q/K/V tiles arrive by TMA, the softmax is computed online (running maximum and sum per row) so the
+// [T, T] score tensor never exists.
+//
+// Reference path: MultiHeadAttention.ForwardCore (src/NeuralSharp/Layers/Attention.cs:46-91): three
+// narrow+permute copies, matmul_f32 (Q.K^T) into a [N*H, T, T] tensor, scale_mask_softmax_f32 with an
+// additive -1e9 mask (one thread per row, PtxKernels.Decoding.cs:24-58), matmul_f32 (P.V), permute back.
+// Skipping the key blocks above the diagonal is exact: exp(-1e9 - max) is 0 in float.  The head
+// split/merge copies disappear because the tensor maps take the (batch, head, position) strides of
+// the caller's buffers.
+//
+// One CTA = one (batch, head, 128 query rows).  192 threads:
+//   warp 0      one lane issues TMA loads: Q once, then K_j and V_j (128 keys each) into a 2-stage ring
+//   warp 1      one lane issues the MMAs: S_{j+1} = Q.K_{j+1}^T is issued before P_j.V_j, so the tensor
+//               cores work on the next scores while the softmax warps handle block j
+//   warps 2..5  softmax: thread r owns query row r (= tensor-memory lane r): reads its 128 scores with
+//               tcgen05.ld, masks, updates max/sum, writes P_j as bf16 into shared memory in the
+//               128-byte-swizzled K-major layout the MMA reads, rescales O in tensor memory when the
+//               row maximum grew by more than 2^8 (otherwise the old reference maximum is kept, which
+//               is exact because the sum and O share it), and at the end divides by the sum and stores
+//               O through shared memory with TMA stores.
+// Tensor memory: S0 at columns [0,128), S1 at [128,256), O at [256,384).
+// Every mbarrier wait is bounded; a wait that runs out reports a status code and the CTA leaves.
+#include <math.h>
+
+#include "ns_common.cuh"
+
+namespace {
+
+constexpr int FA_THREADS = 192;
+constexpr int FA_BLOCK = 128;  // query rows per CTA = keys per block = head_dim
+constexpr uint32_t FA_TILE_BYTES = 128 * 128 * 2;  // 32 KB: two [128 x 64] halves of 16 KB
+constexpr uint32_t FA_HALF_BYTES = 128 * 64 * 2;
+constexpr uint32_t FA_SMEM_BYTES = 1024 + 6 * FA_TILE_BYTES + 256;  // Q, 2 x (K, V), P
+
+struct FaParams {
+    int batch, heads, seq;
+    int causal;
+    float scale_log2;  // scale * log2(e)
+    int* status;
+};
+
+struct FaMaps {
+    CUtensorMap q, k, v;  // box [64 dims, 128 rows]
+    CUtensorMap o;        // box [64 dims, 32 rows] (one softmax warp's rows)
+};
+
+enum { BAR_Q = 0, BAR_K0 = 1, BAR_V0 = 3, BAR_KV_EMPTY0 = 5, BAR_S_FULL0 = 7, BAR_S_FREE0 = 9, BAR_P_FULL = 11, BAR_PV_DONE = 12, BAR_COUNT = 13 };
+
+__global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(const __grid_constant__ FaMaps maps, const FaParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int abort_flag_storage;
+    volatile int* abort_flag = &abort_flag_storage;
+    const uint32_t smem_base = (ns_smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = smem_base;
+    auto k_smem = [&](int s) { return smem_base + FA_TILE_BYTES * (1 + 2 * s); };
+    auto v_smem = [&](int s) { return smem_base + FA_TILE_BYTES * (2 + 2 * s); };
+    const uint32_t p_smem = smem_base + 5 * FA_TILE_BYTES;
+    const uint32_t bar_base = smem_base + 6 * FA_TILE_BYTES;
+    auto bar = [&](int i) { return bar_base + 8u * i; };
+    const uint32_t tmem_slot = bar_base + 8u * BAR_COUNT;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_qt = (p.seq + FA_BLOCK - 1) / FA_BLOCK;
+    // heavy tiles (late query rows see more keys) are scheduled first
+    const int qt = n_qt - 1 - (int)(blockIdx.x / (p.batch * p.heads));
+    const int bh = blockIdx.x % (p.batch * p.heads);
+    const int b = bh / p.heads, h = bh % p.heads;
+    const int q0 = qt * FA_BLOCK;
+    const int n_blocks = p.causal ? qt + 1 : n_qt;
+
+    if (threadIdx.x == 0) {
+        abort_flag_storage = 0;
+        ns_mbar_init(bar(BAR_Q), 1);
+        for (int s = 0; s < 2; s++) {
+            ns_mbar_init(bar(BAR_K0 + s), 1);
+            ns_mbar_init(bar(BAR_V0 + s), 1);
+            ns_mbar_init(bar(BAR_KV_EMPTY0 + s), 1);
+            ns_mbar_init(bar(BAR_S_FULL0 + s), 1);
+            ns_mbar_init(bar(BAR_S_FREE0 + s), 128);
+        }
+        ns_mbar_init(bar(BAR_P_FULL), 128);
+        ns_mbar_init(bar(BAR_PV_DONE), 1);
+        ns_fence_barrier_init();
+        ns_fence_proxy_async();
+        ns_prefetch_tensormap(&maps.q);
+        ns_prefetch_tensormap(&maps.k);
+        ns_prefetch_tensormap(&maps.v);
+        ns_prefetch_tensormap(&maps.o);
+    }
+    if (warp == 1) {
+        ns_tmem_alloc(tmem_slot, 512);
+        ns_tmem_relinquish();
+    }
+    ns_tc_fence_before();
+    __syncthreads();
+    ns_tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+    const int code = 300;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            ns_mbar_expect_tx(bar(BAR_Q), FA_TILE_BYTES);
+            ns_tma_load_4d(q_smem, &maps.q, bar(BAR_Q), 0, q0, h, b);
+            ns_tma_load_4d(q_smem + FA_HALF_BYTES, &maps.q, bar(BAR_Q), 64, q0, h, b);
+            for (int j = 0; j < n_blocks; j++) {
+                const int s = j & 1;
+                if (j >= 2 && !ns_mbar_wait(bar(BAR_KV_EMPTY0 + s), ((j >> 1) - 1) & 1, abort_flag, p.status, code + 1)) break;
+                const int kv0 = j * FA_BLOCK;
+                ns_mbar_expect_tx(bar(BAR_K0 + s), FA_TILE_BYTES);
+                ns_tma_load_4d(k_smem(s), &maps.k, bar(BAR_K0 + s), 0, kv0, h, b);
+                ns_tma_load_4d(k_smem(s) + FA_HALF_BYTES, &maps.k, bar(BAR_K0 + s), 64, kv0, h, b);
+                ns_mbar_expect_tx(bar(BAR_V0 + s), FA_TILE_BYTES);
+                ns_tma_load_4d(v_smem(s), &maps.v, bar(BAR_V0 + s), 0, kv0, h, b);
+                ns_tma_load_4d(v_smem(s) + FA_HALF_BYTES, &maps.v, bar(BAR_V0 + s), 64, kv0, h, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = ns_idesc(1, 1, 0, 0, 128, 128);
+            constexpr uint32_t idesc_pv = ns_idesc(1, 1, 0, 1, 128, 128);
+            const uint64_t desc_k = ns_desc_base(16, 1024);
+            const uint64_t desc_v = ns_desc_base(FA_HALF_BYTES, 1024);  // MN-major: 64-dim halves 16 KB apart, 8 key rows 1 KB apart
+            auto issue_qk = [&](int j) {
+                const uint32_t d_tmem = tmem_base + (j & 1) * 128;
+                const uint32_t kb = k_smem(j & 1);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    const uint32_t off = (kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32;
+                    ns_mma_f16(d_tmem, ns_desc_at(desc_k, q_smem + off), ns_desc_at(desc_k, kb + off), idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                ns_tc_commit(bar(BAR_S_FULL0 + (j & 1)));
+            };
+            bool ok = ns_mbar_wait(bar(BAR_Q), 0, abort_flag, p.status, code + 2);
+            ok = ok && ns_mbar_wait(bar(BAR_K0), 0, abort_flag, p.status, code + 3);
+            if (ok) {
+                ns_tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; j < n_blocks && ok; j++) {
+                const int s = j & 1;
+                if (j + 1 < n_blocks) {
+                    const int jn = j + 1;
+                    ok = ns_mbar_wait(bar(BAR_K0 + (jn & 1)), (jn >> 1) & 1, abort_flag, p.status, code + 3);
+                    if (ok && jn >= 2) ok = ns_mbar_wait(bar(BAR_S_FREE0 + (jn & 1)), ((jn >> 1) - 1) & 1, abort_flag, p.status, code + 4);
+                    if (!ok) break;
+                    ns_tc_fence_after();
+                    issue_qk(jn);
+                }
+                ok = ns_mbar_wait(bar(BAR_P_FULL), j & 1, abort_flag, p.status, code + 5);
+                ok = ok && ns_mbar_wait(bar(BAR_V0 + s), (j >> 1) & 1, abort_flag, p.status, code + 6);
+                if (!ok) break;
+                ns_tc_fence_after();
+                const uint32_t o_tmem = tmem_base + 256;
+                const uint32_t vb = v_smem(s);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    const uint64_t a_desc = ns_desc_at(desc_k, p_smem + (kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32);
+                    const uint64_t b_desc = ns_desc_at(desc_v, vb + kk * (16 * 128));
+                    ns_mma_f16(o_tmem, a_desc, b_desc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                ns_tc_commit(bar(BAR_KV_EMPTY0 + s));
+                ns_tc_commit(bar(BAR_PV_DONE));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax / correction / output
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;          // row inside the tile = tensor-memory lane
+        const int qi = q0 + r;                   // absolute query position
+        const uint32_t lane_addr = tmem_base + (uint32_t(quad * 32) << 16);
+        float m_ref = -INFINITY;                 // reference maximum (raw score units)
+        float l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks && ok; j++) {
+            ok = ns_mbar_wait(bar(BAR_S_FULL0 + (j & 1)), (j >> 1) & 1, abort_flag, p.status, code + 7);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ns_tc_fence_after();
+            uint32_t sbits[128];
+            {
+                uint32_t t0[32], t1[32], t2[32], t3[32];
+                const uint32_t s_addr = lane_addr + (j & 1) * 128;
+                ns_tmem_ld32(s_addr, t0);
+                ns_tmem_ld32(s_addr + 32, t1);
+                ns_tmem_ld32(s_addr + 64, t2);
+                ns_tmem_ld32(s_addr + 96, t3);
+                ns_tc_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c++) { sbits[c] = t0[c]; sbits[32 + c] = t1[c]; sbits[64 + c] = t2[c]; sbits[96 + c] = t3[c]; }
+            }
+            ns_tc_fence_before();
+            ns_mbar_arrive(bar(BAR_S_FREE0 + (j & 1)));
+            // mask: keys after the query (causal) or past the end of the sequence
+            const int kv0 = j * FA_BLOCK;
+            const bool need_mask = (p.causal && kv0 + FA_BLOCK - 1 > q0) || kv0 + FA_BLOCK > p.seq;
+            float mx = -INFINITY;
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < 128; c++) {
+                    const int kj = kv0 + c;
+                    const bool dead = (p.causal && kj > qi) || kj >= p.seq;
+                    if (dead) sbits[c] = 0xFF800000u;  // -inf
+                    mx = fmaxf(mx, __uint_as_float(sbits[c]));
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 128; c++) mx = fmaxf(mx, __uint_as_float(sbits[c]));
+            }
+            // reference maximum: raised only when the row maximum outgrew it by more than 8 / scale_log2
+            float alpha = 1.0f;
+            bool rescale = false;
+            if (mx != -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > 8.0f)) {
+                alpha = m_ref == -INFINITY ? 0.0f : exp2f((m_ref - mx) * p.scale_log2);
+                rescale = m_ref != -INFINITY;
+                m_ref = mx;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+            float sum = 0.0f;
+            uint32_t pk[64];
+#pragma unroll
+            for (int c = 0; c < 128; c += 2) {
+                const float p0 = exp2f((__uint_as_float(sbits[c]) - m_use) * p.scale_log2);
+                const float p1 = exp2f((__uint_as_float(sbits[c + 1]) - m_use) * p.scale_log2);
+                sum += p0 + p1;
+                pk[c >> 1] = ns_f32_to_bf16_bits(p0) | (uint32_t(ns_f32_to_bf16_bits(p1)) << 16);
+            }
+            l_run = l_run * alpha + sum;
+            // P and O belong to the previous P.V until it has completed
+            if (j > 0) {
+                ok = ns_mbar_wait(bar(BAR_PV_DONE), (j - 1) & 1, abort_flag, p.status, code + 8);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ns_tc_fence_after();
+                if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t ob[32];
+                        ns_tmem_ld32(lane_addr + 256 + c * 32, ob);
+                        ns_tc_wait_ld();
+#pragma unroll
+                        for (int t = 0; t < 32; t++) ob[t] = __float_as_uint(__uint_as_float(ob[t]) * alpha);
+                        ns_tmem_st32(lane_addr + 256 + c * 32, ob);
+                    }
+                    ns_tc_wait_st();
+                }
+            }
+            // P_j -> shared memory, K-major halves of 64 keys, 16-byte piece q of row r at q ^ (r & 7)
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+                const uint32_t addr = p_smem + (q >> 3) * FA_HALF_BYTES + r * 128 + (((q & 7) ^ (r & 7)) * 16);
+                ns_st_shared_v4(addr, pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+            }
+            ns_fence_proxy_async();
+            ns_tc_fence_before();
+            ns_mbar_arrive(bar(BAR_P_FULL));
+        }
+        if (ok) {
+            ok = ns_mbar_wait(bar(BAR_PV_DONE), (n_blocks - 1) & 1, abort_flag, p.status, code + 9);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            ns_tc_fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            // O / l -> bf16 -> this warp's 32 rows of the P buffer (free now) -> TMA stores, one per 64-dim half
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t ob[32];
+                ns_tmem_ld32(lane_addr + 256 + c * 32, ob);
+                ns_tc_wait_ld();
+                uint32_t w[16];
+#pragma unroll
+                for (int t = 0; t < 16; t++)
+                    w[t] = ns_f32_to_bf16_bits(__uint_as_float(ob[2 * t]) * inv) | (uint32_t(ns_f32_to_bf16_bits(__uint_as_float(ob[2 * t + 1]) * inv)) << 16);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int piece = (c & 1) * 4 + q;  // 16-byte piece inside the 128-byte row of this half
+                    const uint32_t addr = p_smem + (c >> 1) * FA_HALF_BYTES + r * 128 + ((piece ^ (r & 7)) * 16);
+                    ns_st_shared_v4(addr, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                }
+            }
+            ns_fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && q0 + quad * 32 < p.seq) {
+                ns_tma_store_4d(&maps.o, p_smem + quad * 32 * 128, 0, q0 + quad * 32, h, b);
+                ns_tma_store_4d(&maps.o, p_smem + FA_HALF_BYTES + quad * 32 * 128, 64, q0 + quad * 32, h, b);
+                ns_bulk_commit();
+                ns_bulk_wait<0>();
+            }
+            __syncwarp();
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ns_tc_fence_before();
+    __syncthreads();
+    if (*abort_flag != 0 && threadIdx.x == 0) {
+        long long t0 = clock64();
+        while (clock64() - t0 < 400000) { }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        ns_tc_fence_after();
+        ns_tmem_dealloc(tmem_base, 512);
+    }
+}
+
+int make_map(CUtensorMap* m, uint64_t base, int batch, int heads, int seq, int64_t sb, int64_t sh, int64_t ss, uint32_t box_rows)
+{
+    uint64_t dims[4] = {128, (uint64_t)seq, (uint64_t)heads, (uint64_t)batch};
+    uint64_t strides[3] = {(uint64_t)ss * 2, (uint64_t)sh * 2, (uint64_t)sb * 2};
+    uint32_t box[4] = {64, box_rows, 1, 1};
+    return ns_make_tensor_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, reinterpret_cast<const void*>(base), dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+extern "C" int ns_attention_prefill(ns_device_t h, uint64_t q, uint64_t k, uint64_t v, uint64_t o, int batch, int heads, int seq, int head_dim,
+                                    const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
+                                    float scale, int causal)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(q && k && v && o && q_strides && k_strides && v_strides && o_strides, NS_ERR_ARGUMENT, "ns_attention_prefill: null argument");
+    NS_REQUIRE(head_dim == 128, NS_ERR_ARGUMENT, "ns_attention_prefill: head_dim must be 128 (got %d)", head_dim);
+    NS_REQUIRE(batch > 0 && heads > 0 && seq > 0, NS_ERR_ARGUMENT, "ns_attention_prefill: bad shape");
+    const int n_qt = (seq + FA_BLOCK - 1) / FA_BLOCK;
+    NS_REQUIRE((int64_t)batch * heads * n_qt < (1LL << 31), NS_ERR_ARGUMENT, "ns_attention_prefill: too many tiles");
+    FaMaps maps;
+    rc = make_map(&maps.q, q, batch, heads, seq, q_strides[0], q_strides[1], q_strides[2], 128);
+    if (rc == NS_OK) rc = make_map(&maps.k, k, batch, heads, seq, k_strides[0], k_strides[1], k_strides[2], 128);
+    if (rc == NS_OK) rc = make_map(&maps.v, v, batch, heads, seq, v_strides[0], v_strides[1], v_strides[2], 128);
+    if (rc == NS_OK) rc = make_map(&maps.o, o, batch, heads, seq, o_strides[0], o_strides[1], o_strides[2], 32);
+    if (rc != NS_OK) return rc;
+    FaParams p;
+    p.batch = batch; p.heads = heads; p.seq = seq; p.causal = causal ? 1 : 0;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = d->status_dev;
+    static bool configured[64] = {false};
+    if (!configured[d->ordinal]) {
+        NS_CUDA(cudaFuncSetAttribute(ns_attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM_BYTES));
+        configured[d->ordinal] = true;
+    }
+    ns_attention_prefill_kernel<<<batch * heads * n_qt, FA_THREADS, FA_SMEM_BYTES, d->stream>>>(maps, p);
+    NS_CUDA(cudaGetLastError());
+    return NS_OK;
+}

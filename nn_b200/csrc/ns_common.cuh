@@ -167,6 +167,12 @@ NS_DEVINL void ns_tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int 
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+NS_DEVINL void ns_tma_store_4d(const CUtensorMap* map, uint32_t src, int x, int y, int z, int w)
+{
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w)
+                 : "memory");
+}
 NS_DEVINL void ns_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until at most N of this thread's bulk groups are still reading shared memory
 template <int N>

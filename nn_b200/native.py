@@ -59,6 +59,12 @@ SIGNATURES = {
     "ns_convert": [vp, u64, i32, u64, i32, i64],
     "ns_fill_normal": [vp, u64, i32, i64, u32, f32, f32],
     "ns_fill_ids": [vp, u64, i64, u32, u32],
+    "ns_kv_cache_create": [vp, i32, i32, i32, i32, P(vp)],
+    "ns_kv_cache_destroy": [vp],
+    "ns_kv_cache_pools": [vp, P(u64), P(u64), P(u64)],
+    "ns_kv_append": [vp, vp, u64, u64, i64, u64, i32, u64, i32, i32],
+    "ns_attention_decode": [vp, vp, u64, i64, u64, i64, u64, i32, u64, i32, i32, f32],
+    "ns_attention_prefill": [vp, u64, u64, u64, u64, i32, i32, i32, i32, P(i64), P(i64), P(i64), P(i64), f32, i32],
     "ns_f32_batched_matmul": [vp, u64, u64, u64, i32, i32, i32, i32, i32, i32, f32],
     "ns_f32_scale_mask_softmax": [vp, u64, u64, u64, i32, i32, i32, f32],
     "ns_f32_layernorm_fused": [vp, u64, u64, u64, u64, i32, i32, f32],
