@@ -47,6 +47,9 @@ enum {
     NS_EPI_BIAS_RESIDUAL = 3 /* . + bias[n] + residual[m,n]      (x + Linear(...), Layers/Attention.cs:201-205) */
 };
 
+/* How a Linear layer is divided among tensor-parallel ranks. */
+enum { NS_SPLIT_NONE = 0, NS_SPLIT_COLUMN = 1, NS_SPLIT_ROW = 2 };
+
 typedef struct ns_device_s* ns_device_t;
 typedef struct ns_graph_s* ns_graph_t;
 typedef struct ns_linear_s* ns_linear_t;
@@ -87,6 +90,8 @@ NS_API int ns_d2h(ns_device_t dev, void* dst, uint64_t src, uint64_t bytes);    
 NS_API int ns_h2d_async(ns_device_t dev, uint64_t dst, const void* src, uint64_t bytes);  /* src should be pinned */
 NS_API int ns_d2h_async(ns_device_t dev, void* dst, uint64_t src, uint64_t bytes);
 NS_API int ns_d2d_async(ns_device_t dev, uint64_t dst, uint64_t src, uint64_t bytes);
+/* `rows` rows of width_bytes, pitches in bytes (Backend.Copy2D for raw bytes, Backends/Backend.cs:199). */
+NS_API int ns_d2d_2d_async(ns_device_t dev, uint64_t dst, uint64_t dst_pitch, uint64_t src, uint64_t src_pitch, uint64_t width_bytes, uint64_t rows);
 NS_API int ns_memset32_async(ns_device_t dev, uint64_t dst, uint32_t value, uint64_t count);
 NS_API int ns_host_alloc(uint64_t bytes, void** ptr);   /* pinned host memory */
 NS_API int ns_host_free(void* ptr);
@@ -241,6 +246,51 @@ NS_API int ns_attention_decode(ns_device_t dev, ns_kv_cache_t cache, uint64_t q,
 NS_API int ns_attention_prefill(ns_device_t dev, uint64_t q, uint64_t k, uint64_t v, uint64_t o, int batch, int heads, int seq, int head_dim,
                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
                                 float scale, int causal);
+
+/* ------------------------------------------------------------------------------------------------
+ * Linear objects.  Replace Linear's parameters and ForwardCore (Layers/Linear.cs:25-47): the float [K, N]
+ * weight of the reference (host memory, as read from its weight file) is transposed to one row per output
+ * channel, converted (NS_BF16) or quantised per output channel (NS_I8) and kept on the device; the product and
+ * the bias / bias+GELU / bias+residual kernels that follow it in the reference run as one kernel.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* w_kn: float [K, N] on the host; bias: float [N] on the host or NULL.
+ * split NS_SPLIT_COLUMN: this rank owns N / tp_size outputs.  The columns are taken as col_groups equal blocks and
+ * each rank owns the same slice of every block (col_groups = 3 for a fused [Q|K|V] projection, so a rank gets the
+ * Q, K and V columns of its own heads; 1 otherwise).  split NS_SPLIT_ROW: this rank owns K / tp_size inputs and its
+ * forward yields a partial sum (see ns_bias_residual).  The reference has no counterpart for the split. */
+NS_API int ns_linear_create(ns_device_t dev, int K, int N, int mode, const float* w_kn, const float* bias, int split, int col_groups,
+                            int tp_rank, int tp_size, ns_linear_t* linear);
+NS_API int ns_linear_destroy(ns_linear_t linear);
+NS_API int ns_linear_info(ns_linear_t linear, int* k_local, int* n_local, int* mode, uint64_t* w, uint64_t* w_scale, uint64_t* bias);
+/* y[M, N_local] = epilogue(x . W^T).  NS_I8 layer: x int8 [M, K_local] with x_scale float [M] (from ns_quantize_rows_i8 or
+ * ns_layernorm with NS_I8 output).  NS_BF16 layer: x bf16, x_scale 0.  A row shard (tp_size > 1) takes NS_EPI_NONE only. */
+NS_API int ns_linear_forward(ns_device_t dev, ns_linear_t linear, uint64_t x, uint64_t x_scale, int M, int epilogue, uint64_t residual,
+                             int residual_dtype, int out_dtype, uint64_t y);
+
+/* ------------------------------------------------------------------------------------------------
+ * Tensor parallelism over NCCL.  No counterpart in the reference (single device; Device.cs:54-64).
+ * ------------------------------------------------------------------------------------------------ */
+/* y = (partial + bias[col]) + residual: what a row-parallel layer does after its partial sums (float [rows, cols])
+ * have been reduced across ranks.  bias and residual may be 0. */
+NS_API int ns_bias_residual(ns_device_t dev, uint64_t partial, uint64_t bias, uint64_t residual, int residual_dtype, int64_t rows, int cols,
+                            int out_dtype, uint64_t y);
+/* Greedy token over a vocabulary split by columns: per row the first maximum of this rank's slice
+ * (value, column + col_offset) ... */
+NS_API int ns_argmax_partial(ns_device_t dev, uint64_t x, int rows, int cols, int64_t row_stride, int col_offset, uint64_t out_val, uint64_t out_idx);
+/* ... and the merge of the gathered [parts, rows] pairs: largest value, ties to the smallest column (first maximum wins). */
+NS_API int ns_argmax_merge(ns_device_t dev, uint64_t vals, uint64_t idx, int parts, int rows, uint64_t ids);
+
+/* id128: 128 bytes, made on one rank and given to the others by the host program. */
+NS_API int ns_comm_unique_id(void* id128);
+NS_API int ns_comm_init_rank(ns_device_t dev, const void* id128, int rank, int size, ns_comm_t* comm);
+NS_API int ns_comm_info(ns_comm_t comm, int* rank, int* size, int* nccl_version);
+/* In-place sum over ranks / gather of `count` elements per rank, queued on the device's stream (capturable). */
+NS_API int ns_allreduce(ns_device_t dev, ns_comm_t comm, uint64_t buf, int64_t count, int dtype);
+NS_API int ns_allgather(ns_device_t dev, ns_comm_t comm, uint64_t src, uint64_t dst, int64_t count, int dtype);
+NS_API int ns_comm_async_error(ns_comm_t comm, int* nccl_result);
+NS_API int ns_comm_abort(ns_comm_t comm);     /* after a peer failed: does not wait for the peers */
+NS_API int ns_comm_destroy(ns_comm_t comm);
 
 #ifdef __cplusplus
 }

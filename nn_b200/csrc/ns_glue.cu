@@ -339,3 +339,111 @@ extern "C" int ns_fill_ids(ns_device_t h, uint64_t y, int64_t n, uint32_t seed, 
     NS_CUDA(cudaGetLastError());
     return NS_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Tensor-parallel helpers: what follows the reduction of row-shard partial sums, and the greedy
+// token choice over a vocabulary split across ranks.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+// y = (partial + bias[col]) + residual, the order of the fused epilogue
+__global__ void ns_bias_residual_kernel(const float* __restrict__ partial, const float* __restrict__ bias, const void* __restrict__ residual,
+                                        int residual_dtype, int64_t n, int cols, int out_dtype, void* __restrict__ y)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float v = partial[i];
+        if (bias) v = __fadd_rn(v, bias[i % cols]);
+        if (residual) v = __fadd_rn(v, load_elem(residual, residual_dtype, i));
+        if (out_dtype == NS_F32) reinterpret_cast<float*>(y)[i] = v;
+        else reinterpret_cast<uint16_t*>(y)[i] = ns_f32_to_bf16_bits(v);
+    }
+}
+
+// per row: first maximum of this rank's column slice -> (value, global column index)
+__global__ void __launch_bounds__(ROW_THREADS) ns_argmax_partial_kernel(const float* __restrict__ x, int rows, int cols, int64_t row_stride,
+                                                                        int col_offset, float* __restrict__ out_val, int32_t* __restrict__ out_idx)
+{
+    __shared__ float bv[ROW_THREADS / 32];
+    __shared__ int bi[ROW_THREADS / 32];
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* xs = x + (size_t)r * row_stride;
+        float best = -INFINITY;
+        int idx = 0x7fffffff;
+        for (int j = threadIdx.x; j < cols; j += ROW_THREADS) {
+            float v = xs[j];
+            if (idx == 0x7fffffff || v > best) { best = v; idx = j; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (oi != 0x7fffffff && (idx == 0x7fffffff || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
+        }
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();
+        if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float b = bv[0];
+            int i0 = bi[0];
+            for (int w = 1; w < ROW_THREADS / 32; w++)
+                if (bi[w] != 0x7fffffff && (i0 == 0x7fffffff || bv[w] > b || (bv[w] == b && bi[w] < i0))) { b = bv[w]; i0 = bi[w]; }
+            out_val[r] = b;
+            out_idx[r] = (i0 == 0x7fffffff ? 0 : i0) + col_offset;
+        }
+    }
+}
+
+// vals / idx: [parts, rows]; the largest value wins, ties go to the smallest column index
+__global__ void ns_argmax_merge_kernel(const float* __restrict__ vals, const int32_t* __restrict__ idx, int parts, int rows, int32_t* __restrict__ ids)
+{
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    float b = vals[r];
+    int bi = idx[r];
+    for (int pidx = 1; pidx < parts; pidx++) {
+        const float v = vals[(size_t)pidx * rows + r];
+        const int i = idx[(size_t)pidx * rows + r];
+        if (v > b || (v == b && i < bi)) { b = v; bi = i; }
+    }
+    ids[r] = bi;
+}
+
+}  // namespace
+
+extern "C" int ns_bias_residual(ns_device_t h, uint64_t partial, uint64_t bias, uint64_t residual, int residual_dtype, int64_t rows, int cols,
+                                int out_dtype, uint64_t y)
+{
+    NS_ENTER(h);
+    NS_REQUIRE(partial && y && rows >= 0 && cols > 0, NS_ERR_ARGUMENT, "ns_bias_residual: bad argument");
+    NS_REQUIRE(out_dtype == NS_F32 || out_dtype == NS_BF16, NS_ERR_ARGUMENT, "ns_bias_residual: output must be NS_F32 or NS_BF16");
+    const int64_t n = rows * cols;
+    if (n == 0) return NS_OK;
+    ns_bias_residual_kernel<<<grid_elems(d, n, 256), 256, 0, d->stream>>>(reinterpret_cast<const float*>(partial), reinterpret_cast<const float*>(bias),
+                                                                         reinterpret_cast<const void*>(residual), residual_dtype, n, cols, out_dtype,
+                                                                         reinterpret_cast<void*>(y));
+    NS_CUDA(cudaGetLastError());
+    return NS_OK;
+}
+
+extern "C" int ns_argmax_partial(ns_device_t h, uint64_t x, int rows, int cols, int64_t row_stride, int col_offset, uint64_t out_val, uint64_t out_idx)
+{
+    NS_ENTER(h);
+    NS_REQUIRE(x && out_val && out_idx && rows >= 0 && cols > 0, NS_ERR_ARGUMENT, "ns_argmax_partial: bad argument");
+    if (rows == 0) return NS_OK;
+    ns_argmax_partial_kernel<<<grid_rows(d, rows), ROW_THREADS, 0, d->stream>>>(reinterpret_cast<const float*>(x), rows, cols, row_stride, col_offset,
+                                                                               reinterpret_cast<float*>(out_val), reinterpret_cast<int32_t*>(out_idx));
+    NS_CUDA(cudaGetLastError());
+    return NS_OK;
+}
+
+extern "C" int ns_argmax_merge(ns_device_t h, uint64_t vals, uint64_t idx, int parts, int rows, uint64_t ids)
+{
+    NS_ENTER(h);
+    NS_REQUIRE(vals && idx && ids && parts >= 1 && rows >= 0, NS_ERR_ARGUMENT, "ns_argmax_merge: bad argument");
+    if (rows == 0) return NS_OK;
+    ns_argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, d->stream>>>(reinterpret_cast<const float*>(vals), reinterpret_cast<const int32_t*>(idx), parts,
+                                                                     rows, reinterpret_cast<int32_t*>(ids));
+    NS_CUDA(cudaGetLastError());
+    return NS_OK;
+}

@@ -266,6 +266,17 @@ extern "C" int ns_d2d_async(ns_device_t h, uint64_t dst, uint64_t src, uint64_t 
     return NS_OK;
 }
 
+extern "C" int ns_d2d_2d_async(ns_device_t h, uint64_t dst, uint64_t dst_pitch, uint64_t src, uint64_t src_pitch, uint64_t width_bytes, uint64_t rows)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    if (rows == 0 || width_bytes == 0) return NS_OK;
+    NS_CUDA(cudaMemcpy2DAsync(reinterpret_cast<void*>(dst), dst_pitch, reinterpret_cast<const void*>(src), src_pitch, width_bytes, rows,
+                              cudaMemcpyDeviceToDevice, d->stream));
+    return NS_OK;
+}
+
 __global__ void ns_fill32_kernel(uint32_t* dst, uint32_t value, uint64_t count)
 {
     uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;

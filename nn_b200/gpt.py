@@ -1,0 +1,305 @@
+"""Decoder-only GPT on the int8 / bf16 path: the host side of the reference's generator, over the C ABI.
+
+Mirrors ``CharGpt.Create`` / ``CharGpt.Generate`` (samples/Shared/Gpt/CharGpt.cs:107-124,161-336) and
+``Sequential.ForwardCached`` / ``TransformerEncoderLayer.ForwardCached`` / ``MultiHeadAttention.ForwardCached``
+(src/NeuralSharp/Layers/Sequential.cs:59-80, Layers/Attention.cs:98-118,201-211): pre-LayerNorm blocks
+``x + Attn(LN(x))``, ``x + FF2(GELU(FF1(LN(x))))``, final LayerNorm, head; prefill, then one cached step per token
+replayed as a CUDA graph with the position and the sampled ids living on the device (Layers/Decoding.cs:81-82,
+129-155); when the context is full the last half is re-read from position 0 (CharGpt.cs:276-283).
+
+Arithmetic (the float32-only reference has no counterpart; the CPU oracle in oracle/model.py states the same
+rules): weights int8 per output channel, every Linear input quantised per row from its bf16 value, exact int32
+accumulation, float dequantisation + bias (+GELU, +residual), residual stream / KV cache bf16, LayerNorm and
+softmax statistics float, logits float, greedy token = first maximum.
+
+Tensor parallelism (new; the reference is single-device): QKV and FF1 are split by columns (heads stay whole),
+out-projection and FF2 by rows with a float all-reduce of the partial sums, the head by vocabulary columns with a
+(value, index) merge.  One process per GPU; ``comm`` is a communicator made with ``ns_comm_init_rank``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import native as N
+from .device import Device, Storage
+
+
+@dataclass
+class GptConfig:
+    vocab: int
+    dim: int
+    heads: int
+    layers: int
+    ff_dim: int
+    context: int
+    eps: float = 1e-5
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.heads
+
+
+def _bf16(a: np.ndarray) -> np.ndarray:
+    """float32 -> bf16 bits, round to nearest even (host-side preparation of the embedding tables)."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = u + 0x7FFF + ((u >> 16) & 1)
+    return (u >> 16).astype(np.uint16)
+
+
+class _Linear:
+    def __init__(self, dev: Device, w_kn: np.ndarray, bias, split: int, groups: int, rank: int, size: int, mode: int = N.NS_I8):
+        w = np.ascontiguousarray(w_kn, dtype=np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        h = C.c_void_p()
+        N.call("ns_linear_create", dev.handle, w.shape[0], w.shape[1], mode, w.ctypes.data_as(C.POINTER(C.c_float)),
+               None if b is None else b.ctypes.data_as(C.POINTER(C.c_float)), split, groups, rank, size, C.byref(h))
+        self.handle, self.dev = h, dev
+        k, n, bias_ptr = C.c_int(), C.c_int(), C.c_uint64()
+        N.call("ns_linear_info", h, C.byref(k), C.byref(n), None, None, None, C.byref(bias_ptr))
+        self.k_local, self.n_local, self.bias_ptr = k.value, n.value, bias_ptr.value
+
+    def forward(self, x: int, x_scale: int, m: int, epilogue: int, out_dtype: int, y: int, residual: int = 0, residual_dtype: int = N.NS_BF16):
+        N.call("ns_linear_forward", self.dev.handle, self.handle, C.c_uint64(x), C.c_uint64(x_scale), m, epilogue, C.c_uint64(residual),
+               residual_dtype, out_dtype, C.c_uint64(y))
+
+    def close(self):
+        if self.handle:
+            N.call("ns_linear_destroy", self.handle)
+            self.handle = None
+
+
+class GptW8A8:
+    """weights: dict of float32 arrays in the reference's layouts --
+    tok [V, D], pos [context, D], lnf_g, lnf_b [D], head_w [D, V], head_b [V], and per layer i:
+    ln1_g, ln1_b, qkv_w [D, 3D], qkv_b, out_w [D, D], out_b, ln2_g, ln2_b, ff1_w [D, FF], ff1_b, ff2_w [FF, D], ff2_b
+    under keys f"l{i}.<name>" (Linear.Weight is [in, out], Layers/Linear.cs:25-27).
+    share_layer_weights: build every layer from layer 0's arrays (distinct device copies) -- synthetic benchmarks only.
+    """
+
+    def __init__(self, dev: Device, cfg: GptConfig, weights: dict, batch: int, max_prefill: int, tp_rank: int = 0, tp_size: int = 1,
+                 comm=None, page_size: int = 64, share_layer_weights: bool = False):
+        assert cfg.dim % cfg.heads == 0 and cfg.heads % tp_size == 0 and cfg.ff_dim % tp_size == 0 and cfg.vocab % tp_size == 0
+        assert tp_size == 1 or comm is not None
+        self.dev, self.cfg, self.batch, self.rank, self.tp, self.comm = dev, cfg, batch, tp_rank, tp_size, comm
+        D, FF, V = cfg.dim, cfg.ff_dim, cfg.vocab
+        self.heads_loc, self.d_loc, self.ff_loc, self.v_loc = cfg.heads // tp_size, D // tp_size, FF // tp_size, V // tp_size
+        self.max_rows = batch * max(max_prefill, 1)
+        col, row = N.SPLIT_COLUMN, N.SPLIT_ROW
+        self.tok = dev.from_numpy(_bf16(weights["tok"]))
+        self.pos_table = dev.from_numpy(_bf16(weights["pos"]))
+        self.lnf = (dev.from_numpy(weights["lnf_g"].astype(np.float32)), dev.from_numpy(weights["lnf_b"].astype(np.float32)))
+        self.head = _Linear(dev, weights["head_w"], weights["head_b"], col, 1, tp_rank, tp_size)
+        self.layers = []
+        for i in range(cfg.layers):
+            w = (lambda name, i=i: weights[f"l{0 if share_layer_weights else i}.{name}"])
+            self.layers.append({
+                "ln1": (dev.from_numpy(w("ln1_g").astype(np.float32)), dev.from_numpy(w("ln1_b").astype(np.float32))),
+                "ln2": (dev.from_numpy(w("ln2_g").astype(np.float32)), dev.from_numpy(w("ln2_b").astype(np.float32))),
+                "qkv": _Linear(dev, w("qkv_w"), w("qkv_b"), col, 3, tp_rank, tp_size),
+                "out": _Linear(dev, w("out_w"), w("out_b"), row, 1, tp_rank, tp_size),
+                "ff1": _Linear(dev, w("ff1_w"), w("ff1_b"), col, 1, tp_rank, tp_size),
+                "ff2": _Linear(dev, w("ff2_w"), w("ff2_b"), row, 1, tp_rank, tp_size),
+            })
+        # paged key/value caches, one per layer, identity page table (= the reference's contiguous cache)
+        self.page_size = page_size
+        self.max_pages = (cfg.context + page_size - 1) // page_size
+        self.page_table = dev.from_numpy(np.arange(batch * self.max_pages, dtype=np.int32))
+        self.caches = []
+        for _ in range(cfg.layers):
+            h = C.c_void_p()
+            N.call("ns_kv_cache_create", dev.handle, batch * self.max_pages, page_size, self.heads_loc, cfg.head_dim, C.byref(h))
+            self.caches.append(h)
+        # activations (sized for the longest prefill) and device-side state
+        R = self.max_rows
+        self.x = [dev.empty(R * D, N.NS_BF16), dev.empty(R * D, N.NS_BF16)]
+        self.hq, self.hq_scale = dev.empty(R * max(D, self.ff_loc), N.NS_I8), dev.empty(R)
+        self.qkv = dev.empty(R * 3 * self.d_loc, N.NS_BF16)
+        self.attn = dev.empty(R * self.d_loc, N.NS_BF16)
+        self.ffh = dev.empty(R * self.ff_loc, N.NS_BF16)
+        self.partial = dev.empty(R * D, N.NS_F32) if tp_size > 1 else None
+        self.last = dev.empty(batch * D, N.NS_BF16)
+        self.logits = dev.empty(batch * self.v_loc, N.NS_F32)
+        self.ids = dev.zeros(self.max_rows, N.NS_I32)          # prompt ids during prefill; ids[0:batch] = current tokens while decoding
+        self.pos = dev.zeros(1, N.NS_I32)
+        if tp_size > 1:
+            self.am_val, self.am_idx = dev.empty(batch), dev.empty(batch, N.NS_I32)
+            self.am_vals, self.am_idxs = dev.empty(batch * tp_size), dev.empty(batch * tp_size, N.NS_I32)
+        self.length = 0          # host mirror of the device position (DecodingContext.Length, Layers/Decoding.cs:75)
+        self.graph = None
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------ one pass over `steps` new positions
+    def _reduce_rows(self, lin: _Linear, m: int, x_in: Storage, x_out: Storage):
+        """Row-parallel Linear + residual: fused epilogue on one GPU; partial sums, all-reduce, bias + residual on several."""
+        h, D = self.dev.handle, self.cfg.dim
+        if self.tp == 1:
+            lin.forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS_RESIDUAL, N.NS_BF16, x_out.ptr, residual=x_in.ptr)
+            self._n += 1
+        else:
+            lin.forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_NONE, N.NS_F32, self.partial.ptr)
+            N.call("ns_allreduce", h, self.comm, C.c_uint64(self.partial.ptr), C.c_int64(m * D), N.NS_F32)
+            N.call("ns_bias_residual", h, C.c_uint64(self.partial.ptr), C.c_uint64(lin.bias_ptr), C.c_uint64(x_in.ptr), N.NS_BF16,
+                   C.c_int64(m), D, N.NS_BF16, C.c_uint64(x_out.ptr))
+            self._n += 3
+
+    def _forward(self, steps: int) -> None:
+        """Sequential.ForwardCached for `steps` new positions of every sequence, then the greedy token of the last
+        position into ids[0:batch] and position += steps -- all queued on the device's stream."""
+        cfg, dev, B = self.cfg, self.dev, self.batch
+        h, D, dh, dl = dev.handle, cfg.dim, cfg.head_dim, self.d_loc
+        m = B * steps
+        assert m <= self.max_rows and self.length + steps <= cfg.context, "DecodingContext.BeginStep: capacity exceeded"
+        self._n = 0
+        eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
+        x_in, x_out = self.x
+        N.call("ns_embed_pos", h, self.ids.ptr, self.tok.ptr, self.pos_table.ptr, N.NS_BF16, self.pos.ptr, B, steps, D, cfg.vocab, cfg.context,
+               N.NS_BF16, x_in.ptr)
+        self._n += 1
+        whole_sequence = steps > 1 and self.length == 0 and dh == 128
+        for L, cache in zip(self.layers, self.caches):
+            N.call("ns_layernorm", h, x_in.ptr, N.NS_BF16, L["ln1"][0].ptr, L["ln1"][1].ptr, C.c_int64(m), D, eps, N.NS_I8, self.hq.ptr, self.hq_scale.ptr)
+            L["qkv"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS, N.NS_BF16, self.qkv.ptr)
+            q, k, v = self.qkv.ptr, self.qkv.ptr + 2 * dl, self.qkv.ptr + 4 * dl
+            N.call("ns_kv_append", h, cache, C.c_uint64(k), C.c_uint64(v), C.c_int64(3 * dl), self.page_table.ptr, self.max_pages, self.pos.ptr, B, steps)
+            if whole_sequence:
+                st_in = (C.c_int64 * 3)(steps * 3 * dl, dh, 3 * dl)
+                st_out = (C.c_int64 * 3)(steps * dl, dh, dl)
+                N.call("ns_attention_prefill", h, C.c_uint64(q), C.c_uint64(k), C.c_uint64(v), self.attn.ptr, B, self.heads_loc, steps, dh,
+                       st_in, st_in, st_in, st_out, scale, 1)
+            else:
+                N.call("ns_attention_decode", h, cache, C.c_uint64(q), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
+                       self.max_pages, self.pos.ptr, B, steps, scale)
+            N.call("ns_quantize_rows_i8", h, self.attn.ptr, N.NS_BF16, C.c_int64(m), dl, self.hq.ptr, self.hq_scale.ptr)
+            self._n += 5
+            self._reduce_rows(L["out"], m, x_in, x_out)
+            x_in, x_out = x_out, x_in
+            N.call("ns_layernorm", h, x_in.ptr, N.NS_BF16, L["ln2"][0].ptr, L["ln2"][1].ptr, C.c_int64(m), D, eps, N.NS_I8, self.hq.ptr, self.hq_scale.ptr)
+            L["ff1"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS_GELU, N.NS_BF16, self.ffh.ptr)
+            N.call("ns_quantize_rows_i8", h, self.ffh.ptr, N.NS_BF16, C.c_int64(m), self.ff_loc, self.hq.ptr, self.hq_scale.ptr)
+            self._n += 3
+            self._reduce_rows(L["ff2"], m, x_in, x_out)
+            x_in, x_out = x_out, x_in
+        # only the last position is sampled (Sampling.cs:122); the head is computed for that position alone
+        if steps == 1:
+            last = x_in.ptr
+        else:
+            N.call("ns_d2d_2d_async", h, C.c_uint64(self.last.ptr), C.c_uint64(D * 2), C.c_uint64(x_in.ptr + (steps - 1) * D * 2),
+                   C.c_uint64(steps * D * 2), C.c_uint64(D * 2), C.c_uint64(B))
+            last = self.last.ptr
+        N.call("ns_layernorm", h, C.c_uint64(last), N.NS_BF16, self.lnf[0].ptr, self.lnf[1].ptr, C.c_int64(B), D, eps, N.NS_I8, self.hq.ptr, self.hq_scale.ptr)
+        self.head.forward(self.hq.ptr, self.hq_scale.ptr, B, N.EPI_BIAS, N.NS_F32, self.logits.ptr)
+        if self.tp == 1:
+            N.call("ns_argmax_i32", h, self.logits.ptr, B, cfg.vocab, C.c_int64(cfg.vocab), self.ids.ptr)
+            self._n += 3
+        else:
+            N.call("ns_argmax_partial", h, self.logits.ptr, B, self.v_loc, C.c_int64(self.v_loc), self.rank * self.v_loc, self.am_val.ptr, self.am_idx.ptr)
+            N.call("ns_allgather", h, self.comm, C.c_uint64(self.am_val.ptr), C.c_uint64(self.am_vals.ptr), C.c_int64(B), N.NS_F32)
+            N.call("ns_allgather", h, self.comm, C.c_uint64(self.am_idx.ptr), C.c_uint64(self.am_idxs.ptr), C.c_int64(B), N.NS_I32)
+            N.call("ns_argmax_merge", h, self.am_vals.ptr, self.am_idxs.ptr, self.tp, B, self.ids.ptr)
+            self._n += 6
+        N.call("ns_add_i32", h, self.pos.ptr, steps)
+        self._n += 1
+        self.x = [x_in, x_out]
+
+    # ------------------------------------------------------------------ generator (CharGpt.Generate, CharGpt.cs:231-318)
+    def reset(self) -> None:
+        """DecodingContext.Reset (Layers/Decoding.cs:84-92): position 0; stale cache rows stay masked."""
+        N.call("ns_memset32_async", self.dev.handle, C.c_uint64(self.pos.ptr), 0, C.c_uint64(1))
+        self.length = 0
+
+    def prefill(self, ids: np.ndarray) -> None:
+        """ids [batch, t]: reads t positions from position 0 and samples the next token into ids[0:batch]."""
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        b, t = ids.shape
+        assert b == self.batch
+        self.reset()
+        N.call("ns_h2d", self.dev.handle, C.c_uint64(self.ids.ptr), ids.ctypes.data_as(C.c_void_p), C.c_uint64(ids.nbytes))
+        self._forward(t)
+        self.length = t
+
+    def step(self, use_graph: bool = True) -> None:
+        """One cached decoding step for every sequence; the first call records it as a CUDA graph
+        (DecodingContext.CaptureStep / ReplayStep, Layers/Decoding.cs:129-155)."""
+        assert self.length + 1 <= self.cfg.context, "context is full: re-read the window first"
+        if not use_graph:
+            self._forward(1)
+        else:
+            if self.graph is None:
+                self._forward(1)               # un-captured once: sizes scratch memory, sets kernel attributes
+                self.length += 1
+                self.launches_per_step = self._n
+                self.dev.capture_begin()
+                try:
+                    self._forward(1)
+                except Exception:
+                    N.call("ns_capture_abort", self.dev.handle)
+                    raise
+                self.graph = self.dev.capture_end()
+                return                          # the captured pass did not execute; the un-captured one was this step
+            self.dev.graph_launch(self.graph)
+        self.length += 1
+
+    def read_ids(self) -> np.ndarray:
+        return self.ids.download(count=self.batch).copy()
+
+    def read_logits(self) -> np.ndarray:
+        return self.logits.download((self.batch, self.v_loc))
+
+    def generate(self, prompt: np.ndarray, n_new: int, use_graph: bool = True) -> tuple[np.ndarray, int]:
+        """Greedy decoding of n_new tokens per sequence; returns (tokens [batch, n_new], context resets)."""
+        cfg, B = self.cfg, self.batch
+        history = [list(map(int, row)) for row in np.asarray(prompt)]
+        hist_dev = self.dev.empty(B * max(n_new, 1), N.NS_I32)
+        pending = 0            # tokens sampled on the device and not yet fetched
+        out: list[list[int]] = [[] for _ in range(B)]
+        resets = 0
+
+        def flush():
+            nonlocal pending
+            if pending:
+                got = hist_dev.download((pending, B), count=pending * B)
+                for row in got:
+                    for b in range(B):
+                        history[b].append(int(row[b])); out[b].append(int(row[b]))
+                pending = 0
+
+        def keep_token():
+            nonlocal pending
+            N.call("ns_d2d_async", self.dev.handle, C.c_uint64(hist_dev.ptr + pending * B * 4), C.c_uint64(self.ids.ptr), C.c_uint64(B * 4))
+            pending += 1
+
+        def window(keep):
+            return np.array([h[-keep:] for h in history], dtype=np.int32)
+
+        self.prefill(window(min(len(history[0]), cfg.context - 1)))
+        keep_token()
+        produced = 1
+        while produced < n_new:
+            if self.length >= cfg.context:
+                flush()
+                self.prefill(window(cfg.context // 2))     # window full: re-read the last half from position 0
+                keep_token()
+                resets += 1
+                produced += 1
+                continue
+            self.step(use_graph)
+            keep_token()
+            produced += 1
+        flush()
+        self.dev.synchronize()
+        return np.array(out, dtype=np.int32)[:, :n_new], resets
+
+    def close(self) -> None:
+        if self.graph is not None:
+            self.dev.graph_destroy(self.graph)
+            self.graph = None
+        for c in self.caches:
+            N.call("ns_kv_cache_destroy", c)
+        self.caches = []
+        for L in self.layers:
+            for k in ("qkv", "out", "ff1", "ff2"):
+                L[k].close()
+        self.head.close()

@@ -37,6 +37,7 @@ SIGNATURES = {
     "ns_h2d_async": [vp, u64, vp, u64],
     "ns_d2h_async": [vp, vp, u64, u64],
     "ns_d2d_async": [vp, u64, u64, u64],
+    "ns_d2d_2d_async": [vp, u64, u64, u64, u64, u64, u64],
     "ns_memset32_async": [vp, u64, u32, u64],
     "ns_host_alloc": [u64, P(vp)],
     "ns_host_free": [vp],
@@ -65,6 +66,21 @@ SIGNATURES = {
     "ns_kv_append": [vp, vp, u64, u64, i64, u64, i32, u64, i32, i32],
     "ns_attention_decode": [vp, vp, u64, i64, u64, i64, u64, i32, u64, i32, i32, f32],
     "ns_attention_prefill": [vp, u64, u64, u64, u64, i32, i32, i32, i32, P(i64), P(i64), P(i64), P(i64), f32, i32],
+    "ns_linear_create": [vp, i32, i32, i32, P(f32), P(f32), i32, i32, i32, i32, P(vp)],
+    "ns_linear_destroy": [vp],
+    "ns_linear_info": [vp, P(i32), P(i32), P(i32), P(u64), P(u64), P(u64)],
+    "ns_linear_forward": [vp, vp, u64, u64, i32, i32, u64, i32, i32, u64],
+    "ns_bias_residual": [vp, u64, u64, u64, i32, i64, i32, i32, u64],
+    "ns_argmax_partial": [vp, u64, i32, i32, i64, i32, u64, u64],
+    "ns_argmax_merge": [vp, u64, u64, i32, i32, u64],
+    "ns_comm_unique_id": [vp],
+    "ns_comm_init_rank": [vp, vp, i32, i32, P(vp)],
+    "ns_comm_info": [vp, P(i32), P(i32), P(i32)],
+    "ns_allreduce": [vp, vp, u64, i64, i32],
+    "ns_allgather": [vp, vp, u64, u64, i64, i32],
+    "ns_comm_async_error": [vp, P(i32)],
+    "ns_comm_abort": [vp],
+    "ns_comm_destroy": [vp],
     "ns_f32_batched_matmul": [vp, u64, u64, u64, i32, i32, i32, i32, i32, i32, f32],
     "ns_f32_scale_mask_softmax": [vp, u64, u64, u64, i32, i32, i32, f32],
     "ns_f32_layernorm_fused": [vp, u64, u64, u64, u64, i32, i32, f32],
