@@ -255,12 +255,67 @@ def run_ours(args, rank, world, local_rank):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
-# in profiles/ (null until a capture of this workload exists).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# in profiles/.
+TRAFFIC_BYTES_PER_LAUNCH = 145327360  # 63.33 MB read + 82.00 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
+
+
+def run_case(spec: str):
+    """Small fixed cases for profiler captures (`ncu ... python bench.py --case NAME:ARGS`): three launches of one
+    kernel on device-generated inputs, nothing timed.
+      qmatmul_i8:M            int8 product, K = N = 4096, bias epilogue, f32 out
+      attention_decode:L      batch 64, 32 heads, head_dim 128, cache length L
+      attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
+    """
+    import numpy as np
+    from nn_b200 import native as N
+    from nn_b200.device import Device
+    name, _, arg = spec.partition(":")
+    dev = Device(0)
+    if name == "qmatmul_i8":
+        m = int(arg or M)
+        a, w = dev.empty(m * K, N.NS_I8), dev.empty(NN * K, N.NS_I8)
+        N.call("ns_fill_normal", dev.handle, a.ptr, N.NS_I8, C.c_int64(m * K), 1, 0.0, 40.0)
+        N.call("ns_fill_normal", dev.handle, w.ptr, N.NS_I8, C.c_int64(NN * K), 9, 0.0, 40.0)
+        a_s, w_s, b = dev.empty(m), dev.empty(NN), dev.empty(NN)
+        for t, n_ in ((a_s, m), (w_s, NN), (b, NN)):
+            N.call("ns_fill_normal", dev.handle, t.ptr, N.NS_F32, C.c_int64(n_), 5, 1.0, 0.1)
+        y = dev.empty(m * NN)
+        for _ in range(3):
+            N.call("ns_qmatmul_i8", dev.handle, a.ptr, a_s.ptr, w.ptr, w_s.ptr, b.ptr, 0, 0, m, NN, K, N.EPI_BIAS, N.NS_F32, y.ptr, 0)
+    elif name == "attention_decode":
+        B, heads, dh, L, ps = 64, 32, 128, int(arg or 1024), 64
+        max_pages = (L + ps) // ps
+        h = C.c_void_p()
+        N.call("ns_kv_cache_create", dev.handle, B * max_pages, ps, heads, dh, C.byref(h))
+        kp, vp, nb = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        N.call("ns_kv_cache_pools", h, C.byref(kp), C.byref(vp), C.byref(nb))
+        N.call("ns_fill_normal", dev.handle, kp.value, N.NS_BF16, C.c_int64(nb.value // 2), 2, 0.0, 1.0)
+        N.call("ns_fill_normal", dev.handle, vp.value, N.NS_BF16, C.c_int64(nb.value // 2), 3, 0.0, 1.0)
+        table = dev.from_numpy(np.arange(B * max_pages, dtype=np.int32))
+        pos = dev.from_numpy(np.array([L - 1], np.int32))
+        q, o = dev.empty(B * heads * dh, N.NS_BF16), dev.empty(B * heads * dh, N.NS_BF16)
+        N.call("ns_fill_normal", dev.handle, q.ptr, N.NS_BF16, C.c_int64(B * heads * dh), 1, 0.0, 1.0)
+        for _ in range(3):
+            N.call("ns_attention_decode", dev.handle, h, q.ptr, C.c_int64(heads * dh), o.ptr, C.c_int64(heads * dh), table.ptr, max_pages,
+                   pos.ptr, B, 1, C.c_float(0.0884))
+    elif name == "attention_prefill":
+        B, H, S = 8, 32, int(arg or 2048)
+        n = B * H * S * 128
+        q, k, v, o = (dev.empty(n, N.NS_BF16) for _ in range(4))
+        for t, seed in ((q, 1), (k, 2), (v, 3)):
+            N.call("ns_fill_normal", dev.handle, t.ptr, N.NS_BF16, C.c_int64(n), seed, 0.0, 1.0)
+        st = (C.c_int64 * 3)(H * S * 128, S * 128, 128)
+        for _ in range(3):
+            N.call("ns_attention_prefill", dev.handle, q.ptr, k.ptr, v.ptr, o.ptr, B, H, S, 128, st, st, st, st, C.c_float(0.0884), 1)
+    else:
+        raise SystemExit(f"unknown case {spec}")
+    dev.synchronize()
+    print(json.dumps({"case": spec, "ok": True}))
 
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, help="profiler case, see run_case")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
@@ -271,7 +326,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.case:
+        run_case(args.case)
+    elif args.impl == "reference":
         run_reference(args, rank)
     else:
         run_ours(args, rank, world, local_rank)

@@ -8,6 +8,7 @@
 // CUDA graph.  Errors: every NCCL result other than success becomes NS_ERR_COMM with NCCL's text;
 // ns_comm_abort tears the communicator down without waiting for peers (use it after a peer failed).
 #include <dlfcn.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "ns_common.cuh"
@@ -41,10 +42,14 @@ int load_nccl()
 {
     std::lock_guard<std::mutex> guard(g_nccl_lock);
     if (g_nccl.lib) return NS_OK;
-    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    // An NCCL the process has loaded already (for instance the one bundled with PyTorch) is used as is: the
+    // dynamic loader keeps one library per soname.  NS_B200_NCCL_LIB names a specific file.
+    const char* names[] = {getenv("NS_B200_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
     void* lib = nullptr;
     for (const char* n : names) {
-        lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (n == nullptr || n[0] == 0) continue;
+        lib = dlopen(n, RTLD_NOW | RTLD_NOLOAD);
+        if (!lib) lib = dlopen(n, RTLD_NOW | RTLD_LOCAL);
         if (lib) break;
     }
     NS_REQUIRE(lib != nullptr, NS_ERR_COMM, "NCCL is not available: %s", dlerror());

@@ -52,16 +52,21 @@ extern "C" int ns_linear_create(ns_device_t h, int K, int N, int mode, const flo
     std::vector<float> bl(bias ? N_loc : 0);
     const int group_full = N / col_groups;         // columns per group of the full layer
     const int group_loc = N_loc / col_groups;      // columns per group of this shard (column split)
-    for (int n = 0; n < N_loc; n++) {
-        int src_n = n;
-        if (split == NS_SPLIT_COLUMN) {
-            const int g = n / group_loc, c = n % group_loc;
-            src_n = g * group_full + tp_rank * group_loc + c;
-        }
-        const int k0 = split == NS_SPLIT_ROW ? tp_rank * K_loc : 0;
-        for (int k = 0; k < K_loc; k++) wt[(size_t)n * K_loc + k] = w_kn[(size_t)(k0 + k) * N + src_n];
-        if (bias) bl[n] = bias[src_n];
-    }
+    auto src_col = [&](int n) {
+        if (split != NS_SPLIT_COLUMN) return n;
+        const int g = n / group_loc, c = n % group_loc;
+        return g * group_full + tp_rank * group_loc + c;
+    };
+    const int k0 = split == NS_SPLIT_ROW ? tp_rank * K_loc : 0;
+    // blocked transpose: both arrays are walked in 32 x 32 tiles so neither side strides through memory
+    for (int nb = 0; nb < N_loc; nb += 32)
+        for (int kb = 0; kb < K_loc; kb += 32)
+            for (int n = nb; n < N_loc && n < nb + 32; n++) {
+                const int sn = src_col(n);
+                for (int k = kb; k < K_loc && k < kb + 32; k++) wt[(size_t)n * K_loc + k] = w_kn[(size_t)(k0 + k) * N + sn];
+            }
+    if (bias)
+        for (int n = 0; n < N_loc; n++) bl[n] = bias[src_col(n)];
 
     NsLinear* L = new NsLinear();
     memset(L, 0, sizeof(*L));
