@@ -134,6 +134,15 @@ NS_API int ns_qmatmul_i8(ns_device_t dev, uint64_t aq, uint64_t a_scale, uint64_
                          uint64_t residual, int residual_dtype, int M, int N, int K, int epilogue, int out_dtype,
                          uint64_t y, uint64_t raw_s32);
 
+/* The same product for callers that must not cause a device allocation (a host that records its step into a CUDA
+ * graph with no warm-up run, or one that budgets device memory itself).  No counterpart in the reference.
+ * Partial sums of a K-split product go to a fixed 8 MiB array inside the library instead of the device object's
+ * scratch block: a shape that needs more (k_splits * M * N * 4 bytes) is rejected with NS_ERR_MEMORY.  The first
+ * call on a device looks up the array's address and must come before any stream capture; all calls share the array,
+ * so calls that overlap on the GPU race.  No raw accumulator output. */
+NS_API int ns_qmatmul_i8_static(ns_device_t dev, uint64_t aq, uint64_t a_scale, uint64_t wq, uint64_t w_scale, uint64_t bias,
+                                uint64_t residual, int residual_dtype, int M, int N, int K, int epilogue, int out_dtype, uint64_t y);
+
 /* bf16 product with float accumulation: C[b] = A[b] * op(B[b]); A [m,k] bf16; B [k,n] bf16 (transB = 0)
  * or [n,k] (transB = 1); C [m,n] of out_dtype.  Batch stride = one full matrix, as in the reference.
  * bias [n] float or 0 is added per column when epilogue says so.  k and n multiples of 8. */
