@@ -392,15 +392,25 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tile_coords(p, item, tm, tn, split);
             const int acc = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
-            ok = ns_mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, p.status_base + 4);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            ns_tc_fence_after();
             cx.row0 = tm * BM + quad * 32;
             cx.row = cx.row0 + lane;
             cx.row_ok = cx.row < p.M;
             cx.split = split;
+            // While the tile's MMAs are still running: fetch this row's scale and pull the tile's column scales and
+            // biases into L1 (each tile has other columns, so without this every 32-column chunk below would wait
+            // for a round trip to L2).
             cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok && p.k_splits == 1) ? __ldg(&p.a_scale[cx.row]) : 1.0f;
+            if (p.k_splits == 1 && warp == 2) {
+                const int pc = tn * BN + (lane & 7) * 32;
+                if (lane < BN / 32 && pc < p.N) {
+                    if (KIND == NS_KIND_I8) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.w_scale + pc));
+                    if (p.epilogue != NS_EPI_NONE) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.bias + pc));
+                }
+            }
+            ok = ns_mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, p.status_base + 4);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ns_tc_fence_after();
             const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
             const bool warp_has_rows = cx.row0 < p.M;
             // Two register sets: the tensor-memory load of the next 32 columns is in flight while
