@@ -36,7 +36,7 @@ struct DecodeParams {
     const uint16_t* k_pool;
     const uint16_t* v_pool;
     const int32_t* page_table;
-    int max_pages, page_size, heads;
+    int max_pages, page_size, page_shift, heads;
     const int32_t* pos_dev;
     int batch, steps, splits;
     float scale;
@@ -66,70 +66,89 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8])
     }
 }
 
-// One CTA per (batch, head, new position, split).  DH = head_dim; LPT = DH / 8 lanes cover one row.
+// One CTA per (batch, head, new position, split).  DH = head_dim.  LPR = DH / 32 lanes share one cached row, each
+// lane owning four 16-byte pieces of it (piece i of lane `sub` is piece sub + LPR * i of the row, so the lanes of a
+// row read contiguous 16 * LPR bytes per load).
 template <int DH>
 __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const DecodeParams p)
 {
-    constexpr int LPT = DH / 8;               // lanes per cached position
-    constexpr int TPW = 32 / LPT;             // positions per warp per load
-    constexpr int GROUPS = DEC_THREADS / LPT; // positions in flight per CTA in the P.V phase
+    constexpr int LPR = DH / 32;               // lanes per cached row
+    constexpr int RPW = 32 / LPR;              // rows per warp per load round
+    constexpr int GROUPS = DEC_THREADS / LPR;  // rows in flight per CTA
+    constexpr int U = 2;                       // load rounds in flight
     __shared__ float s_scores[DEC_CHUNK];
     __shared__ float s_red[DEC_THREADS / 32];
     __shared__ float s_acc[GROUPS][DH];
 
+    ns_pdl_wait();
+    ns_pdl_trigger();
     int idx = blockIdx.x;
     const int split = idx % p.splits; idx /= p.splits;
     const int i = idx % p.steps; idx /= p.steps;
     const int h = idx % p.heads;
     const int b = idx / p.heads;
     const int kv_len = p.pos_dev[0] + i + 1;
-    const int per_split = ((kv_len + p.splits - 1) / p.splits + p.page_size - 1) / p.page_size * p.page_size;
+    const int per_split = (((kv_len + p.splits - 1) / p.splits + p.page_size - 1) >> p.page_shift) << p.page_shift;
     const int j0 = split * per_split;
     const int j1 = min(kv_len, j0 + per_split);
     const int row_id = (b * p.heads + h) * p.steps + i;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sub = lane % LPT;  // which 8 dims of the row this lane owns
+    const int sub = threadIdx.x % LPR;       // which pieces of a row this lane owns
+    const int grp = threadIdx.x / LPR;       // row slot of this lane inside the CTA
+    const int page_mask = p.page_size - 1;
 
     float m_run = -INFINITY, l_run = 0.0f;
-    float acc[8];
+    float acc[4][8];
 #pragma unroll
-    for (int d = 0; d < 8; d++) acc[d] = 0.0f;
+    for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int d = 0; d < 8; d++) acc[c][d] = 0.0f;
 
-    float qf[8];
+    float qf[4][8];
     {
-        const uint16_t* qrow = p.q + (size_t)(b * p.steps + i) * p.q_stride + h * DH + sub * 8;
-        unpack8(*reinterpret_cast<const uint4*>(qrow), qf);
+        const uint16_t* qrow = p.q + (size_t)(b * p.steps + i) * p.q_stride + h * DH;
+#pragma unroll
+        for (int c = 0; c < 4; c++) unpack8(*reinterpret_cast<const uint4*>(qrow + (sub + LPR * c) * 8), qf[c]);
     }
     const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
     const size_t slab = (size_t)p.page_size * DH;
+    const size_t head_off = (size_t)h * slab + sub * 8;
+    auto row_ptr = [&](const uint16_t* pool, int j) {
+        const int page = __ldg(&pt[j >> p.page_shift]);
+        return pool + (size_t)page * p.heads * slab + head_off + (size_t)(j & page_mask) * DH;
+    };
 
     for (int c0 = j0; c0 < j1; c0 += DEC_CHUNK) {
         const int c1 = min(j1, c0 + DEC_CHUNK);
-        // ---- scores: s_j = (q . k_j) * scale.  Four rows per lane group are loaded before any is reduced, and the
-        // loop bounds are warp-uniform because the reduction shuffles need every lane.
-        constexpr int SCORE_STRIDE = (DEC_THREADS / 32) * TPW;
-        for (int jb = c0 + warp * TPW; jb < c1; jb += 4 * SCORE_STRIDE) {
-            uint4 kv[4];
+        // ---- scores: s_j = (q . k_j) * scale; U rounds of four loads per lane are in flight before any is used.
+        // Loop bounds are uniform per warp because the reduction shuffles need every lane.
+        for (int jb = c0 + warp * RPW; jb < c1; jb += (DEC_THREADS / 32) * RPW * U) {
+            uint4 kv[U][4];
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int j = jb + u * SCORE_STRIDE + lane / LPT;
-                kv[u] = make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < U; u++) {
+                const int j = jb + u * (DEC_THREADS / 32) * RPW + lane / LPR;
                 if (j < c1) {
-                    const int page = __ldg(&pt[j / p.page_size]);
-                    const uint16_t* krow = p.k_pool + ((size_t)page * p.heads + h) * slab + (size_t)(j % p.page_size) * DH + sub * 8;
-                    kv[u] = __ldg(reinterpret_cast<const uint4*>(krow));
+                    const uint16_t* kr = row_ptr(p.k_pool, j);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) kv[u][c] = __ldg(reinterpret_cast<const uint4*>(kr + LPR * c * 8));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) kv[u][c] = make_uint4(0, 0, 0, 0);
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int j = jb + u * SCORE_STRIDE + lane / LPT;
-                float kf[8];
-                unpack8(kv[u], kf);
+            for (int u = 0; u < U; u++) {
+                const int j = jb + u * (DEC_THREADS / 32) * RPW + lane / LPR;
                 float dot = 0.0f;
 #pragma unroll
-                for (int d = 0; d < 8; d++) dot = fmaf(qf[d], kf[d], dot);
+                for (int c = 0; c < 4; c++) {
+                    float kf[8];
+                    unpack8(kv[u][c], kf);
 #pragma unroll
-                for (int o = LPT / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                    for (int d = 0; d < 8; d++) dot = fmaf(qf[c][d], kf[d], dot);
+                }
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 if (sub == 0 && j < c1) s_scores[j - c0] = dot * p.scale;
             }
         }
@@ -157,41 +176,48 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
         l_run = l_run * alpha + sum;
         m_run = m_new;
 #pragma unroll
-        for (int d = 0; d < 8; d++) acc[d] *= alpha;
-        // ---- o += p_j * v_j ; group g of LPT lanes walks positions g, g + GROUPS, ... four loads in flight
-        for (int jb = c0 + threadIdx.x / LPT; jb < c1; jb += 4 * GROUPS) {
-            uint4 vv[4];
-            float pj[4];
+        for (int c = 0; c < 4; c++)
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int d = 0; d < 8; d++) acc[c][d] *= alpha;
+        // ---- o += p_j * v_j ; row slot `grp` walks rows grp, grp + GROUPS, ...
+        for (int jb = c0 + grp; jb < c1; jb += GROUPS * U) {
+            uint4 vv[U][4];
+            float pj[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
                 const int j = jb + u * GROUPS;
-                vv[u] = make_uint4(0, 0, 0, 0);
                 pj[u] = 0.0f;
                 if (j < c1) {
-                    const int page = __ldg(&pt[j / p.page_size]);
-                    const uint16_t* vrow = p.v_pool + ((size_t)page * p.heads + h) * slab + (size_t)(j % p.page_size) * DH + sub * 8;
-                    vv[u] = __ldg(reinterpret_cast<const uint4*>(vrow));
+                    const uint16_t* vr = row_ptr(p.v_pool, j);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) vv[u][c] = __ldg(reinterpret_cast<const uint4*>(vr + LPR * c * 8));
                     pj[u] = s_scores[j - c0];
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) vv[u][c] = make_uint4(0, 0, 0, 0);
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                float vf[8];
-                unpack8(vv[u], vf);
+            for (int u = 0; u < U; u++)
 #pragma unroll
-                for (int d = 0; d < 8; d++) acc[d] = fmaf(pj[u], vf[d], acc[d]);
-            }
+                for (int c = 0; c < 4; c++) {
+                    float vf[8];
+                    unpack8(vv[u][c], vf);
+#pragma unroll
+                    for (int d = 0; d < 8; d++) acc[c][d] = fmaf(pj[u], vf[d], acc[c][d]);
+                }
         }
         __syncthreads();
     }
     // ---- reduce the GROUPS partial outputs
-    const int g = threadIdx.x / LPT;
 #pragma unroll
-    for (int d = 0; d < 8; d++) s_acc[g][sub * 8 + d] = acc[d];
+    for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int d = 0; d < 8; d++) s_acc[grp][(sub + LPR * c) * 8 + d] = acc[c][d];
     __syncthreads();
     for (int d = threadIdx.x; d < DH; d += DEC_THREADS) {
         float t = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
         for (int gg = 0; gg < GROUPS; gg++) t += s_acc[gg][d];
         if (p.splits == 1) {
             p.o[(size_t)(b * p.steps + i) * p.o_stride + h * DH + d] = ns_f32_to_bf16_bits(t / l_run);
@@ -207,6 +233,8 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
 template <int DH>
 __global__ void ns_attention_combine_kernel(const DecodeParams p)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     const int row_id = blockIdx.x;
     const int i = row_id % p.steps;
     const int h = (row_id / p.steps) % p.heads;
@@ -234,6 +262,8 @@ __global__ void ns_kv_append_kernel(const uint16_t* __restrict__ k, const uint16
                                     uint16_t* v_pool, const int32_t* __restrict__ page_table, int max_pages, int page_size, int heads, int dh,
                                     const int32_t* pos_dev, int batch, int steps)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     const int pos0 = pos_dev[0];
     const int vec = dh / 8;
     const int64_t n = (int64_t)batch * steps * heads * vec;
@@ -256,11 +286,9 @@ template <int DH>
 int launch_decode(NsDevice* d, const DecodeParams& p)
 {
     const int rows = p.batch * p.heads * p.steps;
-    ns_attention_decode_kernel<DH><<<rows * p.splits, DEC_THREADS, 0, d->stream>>>(p);
-    NS_CUDA(cudaGetLastError());
+    NS_CUDA(ns_launch_plain(ns_attention_decode_kernel<DH>, dim3(rows * p.splits), dim3(DEC_THREADS), 0, d->stream, p));
     if (p.splits > 1) {
-        ns_attention_combine_kernel<DH><<<rows, DH < 64 ? 32 : 64, 0, d->stream>>>(p);
-        NS_CUDA(cudaGetLastError());
+        NS_CUDA(ns_launch_plain(ns_attention_combine_kernel<DH>, dim3(rows), dim3(DH < 64 ? 32 : 64), 0, d->stream, p));
     }
     return NS_OK;
 }
@@ -274,6 +302,7 @@ extern "C" int ns_kv_cache_create(ns_device_t h, int num_pages, int page_size, i
     if (rc != NS_OK) return rc;
     NS_REQUIRE(out != nullptr, NS_ERR_ARGUMENT, "ns_kv_cache_create: out handle is null");
     NS_REQUIRE(num_pages > 0 && page_size > 0 && heads > 0, NS_ERR_ARGUMENT, "ns_kv_cache_create: bad shape");
+    NS_REQUIRE((page_size & (page_size - 1)) == 0, NS_ERR_ARGUMENT, "ns_kv_cache_create: page_size must be a power of two (got %d)", page_size);
     NS_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 128, NS_ERR_ARGUMENT, "ns_kv_cache_create: head_dim must be 32, 64 or 128");
     NS_REQUIRE(!d->capturing, NS_ERR_STATE, "ns_kv_cache_create: not allowed while the stream is being captured");
     NsKvCache* c = new NsKvCache();
@@ -330,11 +359,10 @@ extern "C" int ns_kv_append(ns_device_t h, ns_kv_cache_t ch, uint64_t k, uint64_
     if (n == 0) return NS_OK;
     int64_t blocks = (n + 255) / 256;
     if (blocks > (int64_t)d->sm_count * 16) blocks = (int64_t)d->sm_count * 16;
-    ns_kv_append_kernel<<<(unsigned)blocks, 256, 0, d->stream>>>(reinterpret_cast<const uint16_t*>(k), reinterpret_cast<const uint16_t*>(v), src_stride,
+    NS_CUDA(ns_launch_plain(ns_kv_append_kernel, dim3((unsigned)blocks), dim3(256), 0, d->stream, reinterpret_cast<const uint16_t*>(k), reinterpret_cast<const uint16_t*>(v), src_stride,
                                                                 c->k_pool, c->v_pool, reinterpret_cast<const int32_t*>(page_table), max_pages,
                                                                 c->page_size, c->heads, c->head_dim, reinterpret_cast<const int32_t*>(pos_dev), batch,
-                                                                steps);
-    NS_CUDA(cudaGetLastError());
+                                                                steps));
     return NS_OK;
 }
 
@@ -369,6 +397,8 @@ int ns_attention_decode_impl(NsDevice* d, NsKvCache* c, uint64_t q, int64_t q_st
     p.k_pool = c->k_pool; p.v_pool = c->v_pool;
     p.page_table = reinterpret_cast<const int32_t*>(page_table);
     p.max_pages = max_pages; p.page_size = c->page_size; p.heads = c->heads;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < c->page_size) p.page_shift++;
     p.pos_dev = reinterpret_cast<const int32_t*>(pos_dev);
     p.batch = batch; p.steps = steps; p.scale = scale;
     const int rows = batch * c->heads * steps;

@@ -67,6 +67,41 @@ int ns_make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, co
 
 static inline NsDevice* ns_dev(ns_device_t h) { return reinterpret_cast<NsDevice*>(h); }
 
+// Programmatic dependent launch: the kernel may start (set up barriers, allocate tensor memory, prefetch
+// weights) while the previous kernel on the stream is still running; it must execute ns_pdl_wait() before it
+// touches anything the previous kernel wrote or still reads.  NS_B200_PDL=0 in the environment turns it off.
+bool ns_pdl_enabled();
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t ns_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ns_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// Same call shape without the attribute, for kernels that have nothing to do before their inputs are ready (a
+// programmatic edge costs about a microsecond per launch inside a graph and buys them nothing).  They still
+// execute ns_pdl_trigger() so that a product launched after them can start early.
+template <typename... KArgs, typename... Args>
+inline cudaError_t ns_launch_plain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // ---------------------------------------------------------------------------------------------
 // device side
 // ---------------------------------------------------------------------------------------------
@@ -76,6 +111,11 @@ static inline NsDevice* ns_dev(ns_device_t h) { return reinterpret_cast<NsDevice
 
 // About one second at 2 GHz: a wait that lasts this long records an error code and gives up.
 constexpr long long NS_WAIT_LIMIT_CYCLES = 2000000000LL;
+
+// Waits until the kernel this one depends on has completed and its writes are visible (no-op otherwise).
+NS_DEVINL void ns_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel on the stream start its prologue.
+NS_DEVINL void ns_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 NS_DEVINL uint32_t ns_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 

@@ -11,6 +11,7 @@ struct NsGemmParams {
     int k_splits;       // >= 1
     int kb_per_split;   // k-blocks per split
     int tiles_m, tiles_n;
+    int a_rows;         // rows of A fetched per tile (64 when M <= 64, else 128)
     int epilogue;       // NS_EPI_*
     int out_dtype;      // NS_F32 / NS_BF16
     int residual_dtype;
@@ -35,4 +36,4 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
                 void* partial_override = nullptr, size_t partial_override_bytes = 0);
 
 // Tile width / split count the launcher would pick for a shape (also used to size scratch memory).
-void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* tile_n, int* k_splits);
+void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* tile_n, int* k_splits, bool b_is_kn = false);

@@ -310,6 +310,34 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
+            const uint32_t stage_tx = (uint32_t)p.a_rows * BKB + Cfg::B_BYTES;
+            auto load_b = [&](int s, int kb, int tn) {
+                const uint32_t b_dst = smem_base + s * Cfg::STAGE_BYTES + Cfg::A_BYTES;
+                if (!B_MN) {
+                    ns_tma_load_2d(b_dst, &tmB, full_bar(s), kb * ELEMS_PER_KB, tn * BN);
+                } else {
+                    // B stored [K, N]: boxes of 64 columns x 64 rows of K, one per 64 columns of the tile
+#pragma unroll
+                    for (int c = 0; c < BN / 64; c++)
+                        ns_tma_load_2d(b_dst + c * (64 * 128), &tmB, full_bar(s), tn * BN + c * 64, kb * 64);
+                }
+            };
+            // B holds weights, which no kernel of the step writes: the first ring-full of B tiles is requested
+            // before waiting for the previous kernel, so its HBM latency overlaps that kernel's tail.
+            int armed = 0;
+            if ((int)blockIdx.x < n_items) {
+                int tm, tn, split;
+                tile_coords(p, blockIdx.x, tm, tn, split);
+                const int kb0 = split * p.kb_per_split;
+                const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+                armed = min(STAGES, kb1 - kb0);
+                for (int i = 0; i < armed; i++) {
+                    ns_mbar_expect_tx(full_bar(i), stage_tx);
+                    load_b(i, kb0 + i, tn);
+                }
+            }
+            ns_pdl_wait();
+            ns_pdl_trigger();
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -319,20 +347,16 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 int kb0 = split * p.kb_per_split;
                 int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
                 for (int kb = kb0; kb < kb1; kb++) {
-                    ok = ns_mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, p.status_base + 1);
-                    if (!ok) break;
-                    uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
-                    uint32_t b_dst = a_dst + Cfg::A_BYTES;
-                    ns_mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
-                    ns_tma_load_2d(a_dst, &tmA, full_bar(s), kb * ELEMS_PER_KB, tm * BM);
-                    if (!B_MN) {
-                        ns_tma_load_2d(b_dst, &tmB, full_bar(s), kb * ELEMS_PER_KB, tn * BN);
+                    const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
+                    if (armed > 0) {
+                        armed--;   // slot already armed and its B tile on the way
                     } else {
-                        // B stored [K, N]: boxes of 64 columns x 64 rows of K, one per 64 columns of the tile
-#pragma unroll
-                        for (int c = 0; c < BN / 64; c++)
-                            ns_tma_load_2d(b_dst + c * (64 * 128), &tmB, full_bar(s), tn * BN + c * 64, kb * 64);
+                        ok = ns_mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, p.status_base + 1);
+                        if (!ok) break;
+                        ns_mbar_expect_tx(full_bar(s), stage_tx);
+                        load_b(s, kb, tn);
                     }
+                    ns_tma_load_2d(a_dst, &tmA, full_bar(s), kb * ELEMS_PER_KB, tm * BM);
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
             }
@@ -387,6 +411,7 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         cx.nbuf = 0;
         int local = 0;
         bool ok = true;
+        ns_pdl_wait();   // a_scale, residual and every output buffer belong to the previous kernel until it is done
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, local++) {
             int tm, tn, split;
             tile_coords(p, item, tm, tn, split);
@@ -433,9 +458,9 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
             if (lane == 0) ns_mbar_arrive(tempty_bar(acc));
         }
-        // shared memory must stay valid until every queued store has read it, and the kernel's
-        // writes must be complete when it ends
-        if (lane == 0) ns_bulk_wait<0>();
+        // shared memory must stay valid until every queued store has read it; the stores themselves are
+        // complete when the grid is
+        if (lane == 0) ns_bulk_wait_read<0>();
         __syncwarp();
     }
 
@@ -458,6 +483,8 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 template <int KIND>
 __global__ void ns_gemm_splitk_finish_kernel(const NsGemmParams p)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     const int qpr = (p.N + 3) / 4;
     const int64_t quads = (int64_t)p.M * qpr;
     const bool vec = (p.N & 3) == 0;
@@ -517,8 +544,7 @@ int launch_gemm(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, con
     }
     int items = p.tiles_m * p.tiles_n * p.k_splits;
     int grid = items < d->sm_count ? items : d->sm_count;
-    kernel<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, d->stream>>>(tmA, tmB, sm, p);
-    NS_CUDA(cudaGetLastError());
+    NS_CUDA(ns_launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, d->stream, tmA, tmB, sm, p));
     return NS_OK;
 }
 
@@ -535,14 +561,19 @@ int dispatch_bn(NsDevice* d, int bn, const CUtensorMap& tmA, const CUtensorMap& 
 
 }  // namespace
 
-// Tile width and split count: fill the SMs first (wide tiles when there are enough of them), then
-// split K while every split still has at least 4 k-blocks.
-void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* bn_out, int* splits_out)
+// Tile width and split count.  Several row tiles: the widest tile that still fills the SMs, no split.  One row tile
+// (M <= 128, the weight-streaming case): wide tiles, so every k-row of a [K, N] weight is read in long contiguous
+// pieces, and K split until about every SM has a CTA while each split keeps at least 4 k-blocks (measured: the
+// narrow-tile / no-split choice was 1.6x slower on M=8, N=14336, K=4096).
+void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* bn_out, int* splits_out, bool b_is_kn)
 {
     const int tiles_m = (M + BM - 1) / BM;
     int bn = 256;
     if (d->force_bn) {
         bn = d->force_bn == 32 ? 64 : d->force_bn;
+    } else if (tiles_m == 1) {
+        bn = b_is_kn ? 256 : 128;
+        while (bn > 64 && bn / 2 >= N) bn >>= 1;
     } else {
         while (bn > 64 && tiles_m * ((N + bn - 1) / bn) < d->sm_count) bn >>= 1;
         while (bn > 64 && bn / 2 >= N) bn >>= 1;
@@ -556,7 +587,7 @@ void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* b
         int max_by_k = k_blocks / 4;
         if (max_by_k < 1) max_by_k = 1;
         if (splits > max_by_k) splits = max_by_k;
-        if (splits > 16) splits = 16;
+        if (splits > 8) splits = 8;
     }
     if (splits > k_blocks) splits = k_blocks;
     if (splits < 1) splits = 1;
@@ -575,7 +606,7 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     p.M = M; p.N = N; p.K = K;
     p.k_blocks = (int)(((int64_t)K * elsize + BKB - 1) / BKB);
     int bn, splits;
-    ns_gemm_choose_tiling(d, M, N, p.k_blocks, &bn, &splits);
+    ns_gemm_choose_tiling(d, M, N, p.k_blocks, &bn, &splits, b_is_kn);
     p.kb_per_split = (p.k_blocks + splits - 1) / splits;
     p.k_splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
     p.tiles_m = (M + BM - 1) / BM;
@@ -603,7 +634,9 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     {
         uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
         uint64_t strides[1] = {(uint64_t)K * elsize};
-        uint32_t box[2] = {box_k, (uint32_t)BM};
+        // 64 rows are enough for M <= 64: the other accumulator lanes are never stored
+        p.a_rows = M <= 64 ? 64 : BM;
+        uint32_t box[2] = {box_k, (uint32_t)p.a_rows};
         rc = ns_make_tensor_map(&tmA, dt, 2, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != NS_OK) return rc;
     }
@@ -664,9 +697,8 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
         int64_t quads = (int64_t)M * ((N + 3) / 4);
         int64_t blocks = (quads + 255) / 256;
         if (blocks > (int64_t)d->sm_count * 8) blocks = (int64_t)d->sm_count * 8;
-        if (kind == NS_KIND_I8) ns_gemm_splitk_finish_kernel<NS_KIND_I8><<<(unsigned)blocks, 256, 0, d->stream>>>(p);
-        else ns_gemm_splitk_finish_kernel<NS_KIND_BF16><<<(unsigned)blocks, 256, 0, d->stream>>>(p);
-        NS_CUDA(cudaGetLastError());
+        if (kind == NS_KIND_I8) NS_CUDA(ns_launch_plain(ns_gemm_splitk_finish_kernel<NS_KIND_I8>, dim3((unsigned)blocks), dim3(256), 0, d->stream, p));
+        else NS_CUDA(ns_launch_plain(ns_gemm_splitk_finish_kernel<NS_KIND_BF16>, dim3((unsigned)blocks), dim3(256), 0, d->stream, p));
     }
     return NS_OK;
 }

@@ -55,6 +55,8 @@ __device__ __forceinline__ int8_t quant_one(float v, float scale)
 __global__ void __launch_bounds__(ROW_THREADS) ns_quantize_rows_kernel(const void* __restrict__ x, int dtype, int64_t rows, int cols,
                                                                       int8_t* __restrict__ q, float* __restrict__ scale)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     __shared__ float red[ROW_THREADS / 32];
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const size_t base = (size_t)r * cols;
@@ -74,6 +76,8 @@ __global__ void __launch_bounds__(ROW_THREADS) ns_layernorm_kernel(const void* _
                                                                   const float* __restrict__ beta, int64_t rows, int cols, float eps,
                                                                   int out_dtype, void* __restrict__ y, float* __restrict__ y_scale)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     extern __shared__ float rowbuf[];
     __shared__ float red[ROW_THREADS / 32];
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -116,6 +120,8 @@ __global__ void ns_embed_pos_kernel(const int32_t* __restrict__ ids, const void*
                                     const int32_t* __restrict__ pos_dev, int batch, int steps, int dim, int vocab, int max_pos,
                                     int out_dtype, void* __restrict__ y)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     const int p0 = pos_dev ? pos_dev[0] : 0;
     const int64_t n = (int64_t)batch * steps * dim;
     for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
@@ -136,6 +142,8 @@ __global__ void ns_embed_pos_kernel(const int32_t* __restrict__ ids, const void*
 __global__ void __launch_bounds__(ROW_THREADS) ns_argmax_i32_kernel(const float* __restrict__ x, int rows, int cols, int64_t row_stride,
                                                                     int32_t* __restrict__ ids)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     __shared__ float bv[ROW_THREADS / 32];
     __shared__ int bi[ROW_THREADS / 32];
     for (int r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -166,7 +174,12 @@ __global__ void __launch_bounds__(ROW_THREADS) ns_argmax_i32_kernel(const float*
     }
 }
 
-__global__ void ns_add_i32_kernel(int32_t* p, int32_t delta) { p[0] += delta; }
+__global__ void ns_add_i32_kernel(int32_t* p, int32_t delta)
+{
+    ns_pdl_wait();
+    ns_pdl_trigger();
+    p[0] += delta;
+}
 
 __global__ void ns_convert_kernel(const void* __restrict__ x, int in_dtype, void* __restrict__ y, int out_dtype, int64_t n)
 {
@@ -239,7 +252,7 @@ extern "C" int ns_quantize_rows_i8(ns_device_t h, uint64_t x, int in_dtype, int6
     NS_REQUIRE(in_dtype == NS_F32 || in_dtype == NS_BF16, NS_ERR_ARGUMENT, "ns_quantize_rows_i8: input must be NS_F32 or NS_BF16");
     NS_REQUIRE(rows >= 0 && cols > 0, NS_ERR_ARGUMENT, "ns_quantize_rows_i8: bad shape");
     if (rows == 0) return NS_OK;
-    ns_quantize_rows_kernel<<<grid_rows(d, rows), ROW_THREADS, 0, d->stream>>>(reinterpret_cast<const void*>(x), in_dtype, rows, cols,
+    ns_launch_plain(ns_quantize_rows_kernel, dim3(grid_rows(d, rows)), dim3(ROW_THREADS), 0, d->stream, reinterpret_cast<const void*>(x), in_dtype, rows, cols,
                                                                               reinterpret_cast<int8_t*>(q), reinterpret_cast<float*>(scale));
     NS_CUDA(cudaGetLastError());
     return NS_OK;
@@ -261,7 +274,7 @@ extern "C" int ns_layernorm(ns_device_t h, uint64_t x, int in_dtype, uint64_t ga
         NS_CUDA(cudaFuncSetAttribute(ns_layernorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
         configured[d->ordinal] = true;
     }
-    ns_layernorm_kernel<<<grid_rows(d, rows), ROW_THREADS, smem, d->stream>>>(reinterpret_cast<const void*>(x), in_dtype,
+    ns_launch_plain(ns_layernorm_kernel, dim3(grid_rows(d, rows)), dim3(ROW_THREADS), smem, d->stream, reinterpret_cast<const void*>(x), in_dtype,
                                                                              reinterpret_cast<const float*>(gamma), reinterpret_cast<const float*>(beta),
                                                                              rows, cols, eps, out_dtype, reinterpret_cast<void*>(y),
                                                                              reinterpret_cast<float*>(y_scale));
@@ -279,7 +292,7 @@ extern "C" int ns_embed_pos(ns_device_t h, uint64_t ids, uint64_t tok_table, uin
     NS_REQUIRE(batch >= 0 && steps >= 0 && dim > 0 && vocab > 0 && max_pos > 0, NS_ERR_ARGUMENT, "ns_embed_pos: bad shape");
     int64_t n = (int64_t)batch * steps * dim;
     if (n == 0) return NS_OK;
-    ns_embed_pos_kernel<<<grid_elems(d, n, 256), 256, 0, d->stream>>>(reinterpret_cast<const int32_t*>(ids), reinterpret_cast<const void*>(tok_table),
+    ns_launch_plain(ns_embed_pos_kernel, dim3(grid_elems(d, n, 256)), dim3(256), 0, d->stream, reinterpret_cast<const int32_t*>(ids), reinterpret_cast<const void*>(tok_table),
                                                                      reinterpret_cast<const void*>(pos_table), table_dtype,
                                                                      reinterpret_cast<const int32_t*>(pos_dev), batch, steps, dim, vocab, max_pos,
                                                                      out_dtype, reinterpret_cast<void*>(y));
@@ -292,7 +305,7 @@ extern "C" int ns_argmax_i32(ns_device_t h, uint64_t x, int rows, int cols, int6
     NS_ENTER(h);
     NS_REQUIRE(x && ids && rows >= 0 && cols > 0 && row_stride >= cols, NS_ERR_ARGUMENT, "ns_argmax_i32: bad argument");
     if (rows == 0) return NS_OK;
-    ns_argmax_i32_kernel<<<grid_rows(d, rows), ROW_THREADS, 0, d->stream>>>(reinterpret_cast<const float*>(x), rows, cols, row_stride,
+    ns_launch_plain(ns_argmax_i32_kernel, dim3(grid_rows(d, rows)), dim3(ROW_THREADS), 0, d->stream, reinterpret_cast<const float*>(x), rows, cols, row_stride,
                                                                            reinterpret_cast<int32_t*>(ids));
     NS_CUDA(cudaGetLastError());
     return NS_OK;
@@ -302,7 +315,7 @@ extern "C" int ns_add_i32(ns_device_t h, uint64_t counter, int32_t delta)
 {
     NS_ENTER(h);
     NS_REQUIRE(counter != 0, NS_ERR_ARGUMENT, "ns_add_i32: null counter");
-    ns_add_i32_kernel<<<1, 1, 0, d->stream>>>(reinterpret_cast<int32_t*>(counter), delta);
+    ns_launch_plain(ns_add_i32_kernel, dim3(1), dim3(1), 0, d->stream, reinterpret_cast<int32_t*>(counter), delta);
     NS_CUDA(cudaGetLastError());
     return NS_OK;
 }
@@ -350,6 +363,8 @@ namespace {
 __global__ void ns_bias_residual_kernel(const float* __restrict__ partial, const float* __restrict__ bias, const void* __restrict__ residual,
                                         int residual_dtype, int64_t n, int cols, int out_dtype, void* __restrict__ y)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         float v = partial[i];
         if (bias) v = __fadd_rn(v, bias[i % cols]);
@@ -363,6 +378,8 @@ __global__ void ns_bias_residual_kernel(const float* __restrict__ partial, const
 __global__ void __launch_bounds__(ROW_THREADS) ns_argmax_partial_kernel(const float* __restrict__ x, int rows, int cols, int64_t row_stride,
                                                                         int col_offset, float* __restrict__ out_val, int32_t* __restrict__ out_idx)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     __shared__ float bv[ROW_THREADS / 32];
     __shared__ int bi[ROW_THREADS / 32];
     for (int r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -397,6 +414,8 @@ __global__ void __launch_bounds__(ROW_THREADS) ns_argmax_partial_kernel(const fl
 // vals / idx: [parts, rows]; the largest value wins, ties go to the smallest column index
 __global__ void ns_argmax_merge_kernel(const float* __restrict__ vals, const int32_t* __restrict__ idx, int parts, int rows, int32_t* __restrict__ ids)
 {
+    ns_pdl_wait();
+    ns_pdl_trigger();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows) return;
     float b = vals[r];
@@ -419,7 +438,7 @@ extern "C" int ns_bias_residual(ns_device_t h, uint64_t partial, uint64_t bias, 
     NS_REQUIRE(out_dtype == NS_F32 || out_dtype == NS_BF16, NS_ERR_ARGUMENT, "ns_bias_residual: output must be NS_F32 or NS_BF16");
     const int64_t n = rows * cols;
     if (n == 0) return NS_OK;
-    ns_bias_residual_kernel<<<grid_elems(d, n, 256), 256, 0, d->stream>>>(reinterpret_cast<const float*>(partial), reinterpret_cast<const float*>(bias),
+    ns_launch_plain(ns_bias_residual_kernel, dim3(grid_elems(d, n, 256)), dim3(256), 0, d->stream, reinterpret_cast<const float*>(partial), reinterpret_cast<const float*>(bias),
                                                                          reinterpret_cast<const void*>(residual), residual_dtype, n, cols, out_dtype,
                                                                          reinterpret_cast<void*>(y));
     NS_CUDA(cudaGetLastError());
@@ -431,7 +450,7 @@ extern "C" int ns_argmax_partial(ns_device_t h, uint64_t x, int rows, int cols, 
     NS_ENTER(h);
     NS_REQUIRE(x && out_val && out_idx && rows >= 0 && cols > 0, NS_ERR_ARGUMENT, "ns_argmax_partial: bad argument");
     if (rows == 0) return NS_OK;
-    ns_argmax_partial_kernel<<<grid_rows(d, rows), ROW_THREADS, 0, d->stream>>>(reinterpret_cast<const float*>(x), rows, cols, row_stride, col_offset,
+    ns_launch_plain(ns_argmax_partial_kernel, dim3(grid_rows(d, rows)), dim3(ROW_THREADS), 0, d->stream, reinterpret_cast<const float*>(x), rows, cols, row_stride, col_offset,
                                                                                reinterpret_cast<float*>(out_val), reinterpret_cast<int32_t*>(out_idx));
     NS_CUDA(cudaGetLastError());
     return NS_OK;
@@ -442,7 +461,7 @@ extern "C" int ns_argmax_merge(ns_device_t h, uint64_t vals, uint64_t idx, int p
     NS_ENTER(h);
     NS_REQUIRE(vals && idx && ids && parts >= 1 && rows >= 0, NS_ERR_ARGUMENT, "ns_argmax_merge: bad argument");
     if (rows == 0) return NS_OK;
-    ns_argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, d->stream>>>(reinterpret_cast<const float*>(vals), reinterpret_cast<const int32_t*>(idx), parts,
+    ns_launch_plain(ns_argmax_merge_kernel, dim3((rows + 127) / 128), dim3(128), 0, d->stream, reinterpret_cast<const float*>(vals), reinterpret_cast<const int32_t*>(idx), parts,
                                                                      rows, reinterpret_cast<int32_t*>(ids));
     NS_CUDA(cudaGetLastError());
     return NS_OK;

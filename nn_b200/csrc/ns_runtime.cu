@@ -3,6 +3,7 @@
 // (src/NeuralSharp/Backends/Cuda/CudaBackend.cs:48-301, CudaBackend.Decoding.cs:43-130).
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "ns_common.cuh"
@@ -35,6 +36,16 @@ extern "C" const char* ns_error_name(int code)
         case NS_ERR_STATE: return "NS_ERR_STATE";
         default: return "NS_ERR_UNKNOWN";
     }
+}
+
+bool ns_pdl_enabled()
+{
+    static int state = -1;
+    if (state < 0) {
+        const char* e = getenv("NS_B200_PDL");
+        state = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
 }
 
 extern "C" int ns_version(void) { return 100; }
