@@ -10,11 +10,12 @@
 // split/merge copies disappear because the tensor maps take the (batch, head, position) strides of
 // the caller's buffers.
 //
-// One CTA = one (batch, head, 128 query rows).  192 threads:
+// One CTA = one (batch, head, 128 query rows).  320 threads:
 //   warp 0      one lane issues TMA loads: Q once, then K_j and V_j (128 keys each) into a 2-stage ring
 //   warp 1      one lane issues the MMAs: S_{j+1} = Q.K_{j+1}^T is issued before P_j.V_j, so the tensor
 //               cores work on the next scores while the softmax warps handle block j
-//   warps 2..5  softmax: thread r owns query row r (= tensor-memory lane r): reads its 128 scores with
+//   warps 2..9  softmax, two warps per accumulator quadrant (64 key columns each): thread r owns half of query row r
+//               (= tensor-memory lane r): reads its 64 scores with
 //               tcgen05.ld, masks, updates max/sum, writes P_j as bf16 into shared memory in the
 //               128-byte-swizzled K-major layout the MMA reads, rescales O in tensor memory when the
 //               row maximum grew by more than 2^8 (otherwise the old reference maximum is kept, which
@@ -28,11 +29,11 @@
 
 namespace {
 
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;  // producer warp, MMA warp, 8 softmax warps
 constexpr int FA_BLOCK = 128;  // query rows per CTA = keys per block = head_dim
 constexpr uint32_t FA_TILE_BYTES = 128 * 128 * 2;  // 32 KB: two [128 x 64] halves of 16 KB
 constexpr uint32_t FA_HALF_BYTES = 128 * 64 * 2;
-constexpr uint32_t FA_SMEM_BYTES = 1024 + 6 * FA_TILE_BYTES + 256;  // Q, 2 x (K, V), P
+constexpr uint32_t FA_SMEM_BYTES = 1024 + 6 * FA_TILE_BYTES + 256 + 2048;  // Q, 2 x (K, V), P, barriers, row-maximum exchange
 
 struct FaParams {
     int batch, heads, seq;
@@ -46,7 +47,7 @@ struct FaMaps {
     CUtensorMap o;        // box [64 dims, 32 rows] (one softmax warp's rows)
 };
 
-enum { BAR_Q = 0, BAR_K0 = 1, BAR_V0 = 3, BAR_KV_EMPTY0 = 5, BAR_S_FULL0 = 7, BAR_S_FREE0 = 9, BAR_P_FULL = 11, BAR_PV_DONE = 12, BAR_COUNT = 13 };
+enum { BAR_Q = 0, BAR_K0 = 1, BAR_V0 = 3, BAR_KV_EMPTY0 = 5, BAR_S_FULL0 = 7, BAR_S_FREE0 = 9, BAR_P_FULL = 11, BAR_PV_DONE = 12, BAR_PAIR0 = 13, BAR_COUNT = 17 };
 
 __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(const __grid_constant__ FaMaps maps, const FaParams p)
 {
@@ -79,9 +80,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
             ns_mbar_init(bar(BAR_V0 + s), 1);
             ns_mbar_init(bar(BAR_KV_EMPTY0 + s), 1);
             ns_mbar_init(bar(BAR_S_FULL0 + s), 1);
-            ns_mbar_init(bar(BAR_S_FREE0 + s), 128);
+            ns_mbar_init(bar(BAR_S_FREE0 + s), 256);
         }
-        ns_mbar_init(bar(BAR_P_FULL), 128);
+        ns_mbar_init(bar(BAR_P_FULL), 256);
+        for (int q = 0; q < 4; q++) ns_mbar_init(bar(BAR_PAIR0 + q), 64);
         ns_mbar_init(bar(BAR_PV_DONE), 1);
         ns_fence_barrier_init();
         ns_fence_proxy_async();
@@ -170,47 +172,70 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
         }
     } else {
         // ------------------------------------------------------------ softmax / correction / output
+        // Two warps per accumulator quadrant: warps 2..5 own key columns 0..63 of their 32 rows, warps 6..9 columns
+        // 64..127 (a warp reaches only the tensor-memory lanes of quadrant warp % 4).  With one warp per scheduler
+        // every dependent instruction's latency was exposed; two hide each other's.  The two threads of a row
+        // exchange their partial row maximum through shared memory once per key block.
         const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;        // which 64 key columns / 64 output dims this thread owns
         const int r = quad * 32 + lane;          // row inside the tile = tensor-memory lane
         const int qi = q0 + r;                   // absolute query position
         const uint32_t lane_addr = tmem_base + (uint32_t(quad * 32) << 16);
-        float m_ref = -INFINITY;                 // reference maximum (raw score units)
-        float l_run = 0.0f;
+        const uint32_t xch = bar_base + 8u * 24;                     // float [2 buffers][2 halves][128 rows]
+        auto xch_addr = [&](int buf, int hf) { return xch + ((buf * 2 + hf) * 128 + r) * 4; };
+        float m_ref = -INFINITY;                 // reference maximum (raw score units), identical in both threads of a row
+        float l_run = 0.0f;                      // this thread's share of the row sum
+        uint32_t pair_phase = 0;
         bool ok = true;
         for (int j = 0; j < n_blocks && ok; j++) {
             ok = ns_mbar_wait(bar(BAR_S_FULL0 + (j & 1)), (j >> 1) & 1, abort_flag, p.status, code + 7);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             ns_tc_fence_after();
-            uint32_t sbits[128];
+            uint32_t sbits[64];
             {
-                uint32_t t0[32], t1[32], t2[32], t3[32];
-                const uint32_t s_addr = lane_addr + (j & 1) * 128;
+                uint32_t t0[32], t1[32];
+                const uint32_t s_addr = lane_addr + (j & 1) * 128 + half * 64;
                 ns_tmem_ld32(s_addr, t0);
                 ns_tmem_ld32(s_addr + 32, t1);
-                ns_tmem_ld32(s_addr + 64, t2);
-                ns_tmem_ld32(s_addr + 96, t3);
                 ns_tc_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 32; c++) { sbits[c] = t0[c]; sbits[32 + c] = t1[c]; sbits[64 + c] = t2[c]; sbits[96 + c] = t3[c]; }
+                for (int c = 0; c < 32; c++) { sbits[c] = t0[c]; sbits[32 + c] = t1[c]; }
             }
             ns_tc_fence_before();
             ns_mbar_arrive(bar(BAR_S_FREE0 + (j & 1)));
             // mask: keys after the query (causal) or past the end of the sequence
-            const int kv0 = j * FA_BLOCK;
-            const bool need_mask = (p.causal && kv0 + FA_BLOCK - 1 > q0) || kv0 + FA_BLOCK > p.seq;
+            const int kv0 = j * FA_BLOCK + half * 64;
+            const bool need_mask = (p.causal && kv0 + 63 > q0) || kv0 + 64 > p.seq;
             float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 128; c++) {
+                for (int c = 0; c < 64; c++) {
                     const int kj = kv0 + c;
                     const bool dead = (p.causal && kj > qi) || kj >= p.seq;
                     if (dead) sbits[c] = 0xFF800000u;  // -inf
                     mx = fmaxf(mx, __uint_as_float(sbits[c]));
                 }
             } else {
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int c = 0; c < 128; c++) mx = fmaxf(mx, __uint_as_float(sbits[c]));
+                for (int c = 0; c < 64; c += 4) {
+                    m4[0] = fmaxf(m4[0], __uint_as_float(sbits[c])); m4[1] = fmaxf(m4[1], __uint_as_float(sbits[c + 1]));
+                    m4[2] = fmaxf(m4[2], __uint_as_float(sbits[c + 2])); m4[3] = fmaxf(m4[3], __uint_as_float(sbits[c + 3]));
+                }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            }
+            // row maximum over both halves
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch_addr(j & 1, half)), "f"(mx) : "memory");
+            ns_mbar_arrive(bar(BAR_PAIR0 + quad));
+            ok = ns_mbar_wait(bar(BAR_PAIR0 + quad), pair_phase, abort_flag, p.status, code + 10);
+            pair_phase ^= 1u;
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            {
+                float other;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(xch_addr(j & 1, half ^ 1)) : "memory");
+                mx = fmaxf(mx, other);
             }
             // reference maximum: raised only when the row maximum outgrew it by more than 8 / scale_log2
             float alpha = 1.0f;
@@ -221,16 +246,20 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
                 m_ref = mx;
             }
             const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-            float sum = 0.0f;
-            uint32_t pk[64];
+            const float neg_m = -m_use * p.scale_log2;
+            float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 128; c += 2) {
-                const float p0 = exp2f((__uint_as_float(sbits[c]) - m_use) * p.scale_log2);
-                const float p1 = exp2f((__uint_as_float(sbits[c + 1]) - m_use) * p.scale_log2);
-                sum += p0 + p1;
+            for (int c = 0; c < 64; c += 4) {
+                const float p0 = exp2f(fmaf(__uint_as_float(sbits[c]), p.scale_log2, neg_m));
+                const float p1 = exp2f(fmaf(__uint_as_float(sbits[c + 1]), p.scale_log2, neg_m));
+                const float p2 = exp2f(fmaf(__uint_as_float(sbits[c + 2]), p.scale_log2, neg_m));
+                const float p3 = exp2f(fmaf(__uint_as_float(sbits[c + 3]), p.scale_log2, neg_m));
+                s4[0] += p0; s4[1] += p1; s4[2] += p2; s4[3] += p3;
                 pk[c >> 1] = ns_f32_to_bf16_bits(p0) | (uint32_t(ns_f32_to_bf16_bits(p1)) << 16);
+                pk[(c >> 1) + 1] = ns_f32_to_bf16_bits(p2) | (uint32_t(ns_f32_to_bf16_bits(p3)) << 16);
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
             // P and O belong to the previous P.V until it has completed
             if (j > 0) {
                 ok = ns_mbar_wait(bar(BAR_PV_DONE), (j - 1) & 1, abort_flag, p.status, code + 8);
@@ -239,21 +268,21 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
                 ns_tc_fence_after();
                 if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
+                    for (int c = 0; c < 2; c++) {
                         uint32_t ob[32];
-                        ns_tmem_ld32(lane_addr + 256 + c * 32, ob);
+                        ns_tmem_ld32(lane_addr + 256 + half * 64 + c * 32, ob);
                         ns_tc_wait_ld();
 #pragma unroll
                         for (int t = 0; t < 32; t++) ob[t] = __float_as_uint(__uint_as_float(ob[t]) * alpha);
-                        ns_tmem_st32(lane_addr + 256 + c * 32, ob);
+                        ns_tmem_st32(lane_addr + 256 + half * 64 + c * 32, ob);
                     }
                     ns_tc_wait_st();
                 }
             }
             // P_j -> shared memory, K-major halves of 64 keys, 16-byte piece q of row r at q ^ (r & 7)
 #pragma unroll
-            for (int q = 0; q < 16; q++) {
-                const uint32_t addr = p_smem + (q >> 3) * FA_HALF_BYTES + r * 128 + (((q & 7) ^ (r & 7)) * 16);
+            for (int q = 0; q < 8; q++) {
+                const uint32_t addr = p_smem + half * FA_HALF_BYTES + r * 128 + ((q ^ (r & 7)) * 16);
                 ns_st_shared_v4(addr, pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
             }
             ns_fence_proxy_async();
@@ -265,13 +294,23 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
+            // total row sum = the two threads' shares (both used the same reference maximum throughout)
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch_addr(n_blocks & 1, half)), "f"(l_run) : "memory");
+            ns_mbar_arrive(bar(BAR_PAIR0 + quad));
+            ok = ns_mbar_wait(bar(BAR_PAIR0 + quad), pair_phase, abort_flag, p.status, code + 10);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            float other;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(xch_addr(n_blocks & 1, half ^ 1)) : "memory");
             ns_tc_fence_after();
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            // O / l -> bf16 -> this warp's 32 rows of the P buffer (free now) -> TMA stores, one per 64-dim half
+            const float l_tot = l_run + other;
+            const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+            // O / l -> bf16 -> this warp's 32 rows of its 64-dim half of the P buffer (free now) -> one TMA store
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
                 uint32_t ob[32];
-                ns_tmem_ld32(lane_addr + 256 + c * 32, ob);
+                ns_tmem_ld32(lane_addr + 256 + half * 64 + c * 32, ob);
                 ns_tc_wait_ld();
                 uint32_t w[16];
 #pragma unroll
@@ -279,18 +318,17 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
                     w[t] = ns_f32_to_bf16_bits(__uint_as_float(ob[2 * t]) * inv) | (uint32_t(ns_f32_to_bf16_bits(__uint_as_float(ob[2 * t + 1]) * inv)) << 16);
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const int piece = (c & 1) * 4 + q;  // 16-byte piece inside the 128-byte row of this half
-                    const uint32_t addr = p_smem + (c >> 1) * FA_HALF_BYTES + r * 128 + ((piece ^ (r & 7)) * 16);
+                    const int piece = c * 4 + q;  // 16-byte piece inside the 128-byte row of this half
+                    const uint32_t addr = p_smem + half * FA_HALF_BYTES + r * 128 + ((piece ^ (r & 7)) * 16);
                     ns_st_shared_v4(addr, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
                 }
             }
             ns_fence_proxy_async();
             __syncwarp();
             if (lane == 0 && q0 + quad * 32 < p.seq) {
-                ns_tma_store_4d(&maps.o, p_smem + quad * 32 * 128, 0, q0 + quad * 32, h, b);
-                ns_tma_store_4d(&maps.o, p_smem + FA_HALF_BYTES + quad * 32 * 128, 64, q0 + quad * 32, h, b);
+                ns_tma_store_4d(&maps.o, p_smem + half * FA_HALF_BYTES + quad * 32 * 128, half * 64, q0 + quad * 32, h, b);
                 ns_bulk_commit();
-                ns_bulk_wait<0>();
+                ns_bulk_wait_read<0>();
             }
             __syncwarp();
         }
