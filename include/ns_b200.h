@@ -221,6 +221,20 @@ NS_API int ns_f32_permute(ns_device_t dev, uint64_t x, uint64_t y, const int* ou
 /* [199] dst[dstOffset + r*dstStride + c] (+)= src[srcOffset + r*srcStride + c] */
 NS_API int ns_f32_copy2d(ns_device_t dev, uint64_t src, int64_t srcOffset, int srcStride, uint64_t dst, int64_t dstOffset, int dstStride,
                          int rows, int cols, int accumulate);
+/* [248] SampleRows (kernel sample_rows_f32, Backends/Cuda/PtxKernels.Decoding.cs:170-350; CPU twin
+ * Backends/Cpu/CpuBackend.Decoding.cs:114-245).  Row r reads logits[r * rowStride + rowOffset + j], j < vocabulary;
+ * writes ids[r] (float-encoded) and 13 statistics at stats[(step[0] * rows + r) * 13]: id, probability, entropy in
+ * bits, five (alternative id, probability) pairs (-1, 0 when fewer are kept).  step[0] is a float in device memory,
+ * so a recorded graph stays valid.  temperature is floored at 1e-3; topK 0 = all; topP 1 = off; minP 0 = off. */
+NS_API int ns_f32_sample_rows(ns_device_t dev, uint64_t logits, uint64_t ids, uint64_t stats, uint64_t step, int rows, int vocabulary,
+                              int rowStride, int rowOffset, float temperature, int topK, float topP, float minP, uint32_t seed);
+/* [257] PenalizeRows (penalize_rows_f32, PtxKernels.Decoding.cs:352-433): work[r,:] = logits row r, then every distinct
+ * token among the last min(length[0], lastN, capacity) entries of history[r,:] (a ring indexed modulo capacity) gets
+ * x = x > 0 ? x / repeat : x * repeat; x -= presence + frequency * occurrences. */
+NS_API int ns_f32_penalize_rows(ns_device_t dev, uint64_t logits, uint64_t work, uint64_t history, uint64_t length, int rows, int vocabulary,
+                                int rowStride, int rowOffset, int capacity, int lastN, float repeat, float presence, float frequency);
+/* [261] HistoryPush (history_push_f32, PtxKernels.Decoding.cs:435-447): history[r, length[0] % capacity] = ids[r]. */
+NS_API int ns_f32_history_push(ns_device_t dev, uint64_t ids, uint64_t history, uint64_t length, int rows, int capacity);
 
 /* ------------------------------------------------------------------------------------------------
  * Key/value cache and attention.  Replaces KeyValueCache + Tensor.WriteKeyValues (Layers/Decoding.cs:14-35,

@@ -106,6 +106,20 @@ class NsB200Backend:
     def KeyValueWrite(self, source: Storage, cache: Storage, position: Storage, heads: int, steps: int, capacity: int, dim: int) -> None:
         N.call("ns_f32_key_value_write", self._h, source.ptr, cache.ptr, position.ptr, heads, steps, capacity, dim)
 
+    # ---- on-device sampling (Backend.cs:240-261)
+    def SampleRows(self, logits: Storage, ids: Storage, stats: Storage, step: Storage, rows: int, vocabulary: int, rowStride: int, rowOffset: int,
+                   temperature: float, topK: int, topP: float, minP: float, seed: int) -> None:
+        N.call("ns_f32_sample_rows", self._h, logits.ptr, ids.ptr, stats.ptr, step.ptr, rows, vocabulary, rowStride, rowOffset,
+               C.c_float(temperature), topK, C.c_float(topP), C.c_float(minP), C.c_uint32(seed & 0xFFFFFFFF))
+
+    def PenalizeRows(self, logits: Storage, work: Storage, history: Storage, length: Storage, rows: int, vocabulary: int, rowStride: int,
+                     rowOffset: int, capacity: int, lastN: int, repeat: float, presence: float, frequency: float) -> None:
+        N.call("ns_f32_penalize_rows", self._h, logits.ptr, work.ptr, history.ptr, length.ptr, rows, vocabulary, rowStride, rowOffset,
+               capacity, lastN, C.c_float(repeat), C.c_float(presence), C.c_float(frequency))
+
+    def HistoryPush(self, ids: Storage, history: Storage, length: Storage, rows: int, capacity: int) -> None:
+        N.call("ns_f32_history_push", self._h, ids.ptr, history.ptr, length.ptr, rows, capacity)
+
     # ---- graphs (Backend.cs:266-281)
     SupportsGraphs = True
 

@@ -97,6 +97,9 @@ SIGNATURES = {
     "ns_f32_argmax_strided": [vp, u64, u64, i32, i32, i64, i64],
     "ns_f32_permute": [vp, u64, u64, P(i32), P(i32), i32, i32],
     "ns_f32_copy2d": [vp, u64, i64, i32, u64, i64, i32, i32, i32, i32],
+    "ns_f32_sample_rows": [vp, u64, u64, u64, u64, i32, i32, i32, i32, f32, i32, f32, f32, u32],
+    "ns_f32_penalize_rows": [vp, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, f32, f32, f32],
+    "ns_f32_history_push": [vp, u64, u64, u64, i32, i32],
 }
 
 _SPECIAL = {

@@ -529,3 +529,125 @@ ORC_API void orc_attention_slice(const float *q, const float *k, const float *v,
         free(s);
     }
 }
+
+/* ------------------------------------------------------------------------------------------------
+ * Token sampler (src/NeuralSharp/Backends/Cpu/CpuBackend.Decoding.cs:114-292), float32, restated
+ * pass for pass: scaled scores s = z / max(T, 1e-3); top-k threshold = k-th largest distinct score;
+ * min-p threshold max + ln(minP); top-p by 24 bisection steps on the score; e = exp(s - max) above the
+ * threshold; first index whose running sum exceeds u * sum with u = CounterRandom.Uniform(seed, step,
+ * row); 13 statistics per token: id, probability, entropy in bits, five (alternative id, probability)
+ * pairs (-1, 0 when fewer exist).
+ * ------------------------------------------------------------------------------------------------ */
+ORC_API void orc_sample_rows(const float *logits, float *ids, float *stats, const float *step, int rows, int vocabulary,
+                             int rowStride, int rowOffset, float temperature, int topK, float topP, float minP, uint32_t seed)
+{
+    uint32_t stepNumber = (uint32_t)step[0];
+    float invT = 1.0f / fmaxf(temperature, 1e-3f);
+    float *e = (float *)malloc(sizeof(float) * vocabulary);
+    for (int r = 0; r < rows; r++) {
+        const float *z = logits + (size_t)r * rowStride + rowOffset;
+        float max = -INFINITY;
+        for (int j = 0; j < vocabulary; j++) max = fmaxf(max, z[j] * invT);
+        float threshold = -INFINITY;
+        if (topK > 0 && topK < vocabulary) {
+            threshold = INFINITY;
+            for (int k = 0; k < topK; k++) {
+                float next = -INFINITY;
+                for (int j = 0; j < vocabulary; j++) {
+                    float s = z[j] * invT;
+                    if (s < threshold && s > next) next = s;
+                }
+                threshold = next;
+            }
+        }
+        if (minP > 0.0f) threshold = fmaxf(threshold, max + logf(minP));
+        if (topP > 0.0f && topP < 1.0f) {
+            float total = 0.0f;
+            for (int j = 0; j < vocabulary; j++) {
+                float s = z[j] * invT;
+                total += s >= threshold ? expf(s - max) : 0.0f;
+            }
+            float goal = total * topP, lo = fmaxf(max - 40.0f, threshold), hi = max;
+            for (int it = 0; it < 24; it++) {
+                float mid = (lo + hi) * 0.5f, mass = 0.0f;
+                for (int j = 0; j < vocabulary; j++) {
+                    float s = z[j] * invT;
+                    mass += (s >= threshold && s >= mid) ? expf(s - max) : 0.0f;
+                }
+                if (mass >= goal) lo = mid; else hi = mid;
+            }
+            threshold = lo;
+        }
+        float sum = 0.0f;
+        for (int j = 0; j < vocabulary; j++) {
+            float s = z[j] * invT;
+            e[j] = s >= threshold ? expf(s - max) : 0.0f;
+            sum += e[j];
+        }
+        float target = orc_counter_uniform(seed, stepNumber, (uint32_t)r) * sum;
+        int chosen = -1;
+        float cumulative = 0.0f;
+        for (int j = 0; j < vocabulary; j++) {
+            if (e[j] > 0.0f) {
+                chosen = j;
+                cumulative += e[j];
+                if (cumulative > target) break;
+            }
+        }
+        float entropy = 0.0f;
+        for (int j = 0; j < vocabulary; j++)
+            if (e[j] > 0.0f) { float p = e[j] / sum; entropy -= p * log2f(p); }
+        ids[r] = (float)chosen;
+        size_t o = ((size_t)stepNumber * rows + r) * 13;
+        stats[o] = (float)chosen;
+        stats[o + 1] = e[chosen] / sum;
+        stats[o + 2] = entropy;
+        int taken[5];
+        for (int a = 0; a < 5; a++) {
+            int best = -1;
+            for (int j = 0; j < vocabulary; j++) {
+                if (e[j] > 0.0f && (best < 0 || e[j] > e[best])) {
+                    int used = 0;
+                    for (int t = 0; t < a; t++) used |= taken[t] == j;
+                    if (!used) best = j;
+                }
+            }
+            taken[a] = best;
+            stats[o + 3 + 2 * a] = (float)best;
+            stats[o + 4 + 2 * a] = best < 0 ? 0.0f : e[best] / sum;
+        }
+    }
+    free(e);
+}
+
+/* PenalizeRows, CpuBackend.Decoding.cs:247-282. */
+ORC_API void orc_penalize_rows(const float *logits, float *work, const float *history, const float *length, int rows, int vocabulary,
+                               int rowStride, int rowOffset, int capacity, int lastN, float repeat, float presence, float frequency)
+{
+    uint32_t len = (uint32_t)length[0];
+    uint32_t lim = (uint32_t)(lastN < capacity ? lastN : capacity);
+    int n = (int)(len < lim ? len : lim);
+    for (int r = 0; r < rows; r++) {
+        float *w = work + (size_t)r * vocabulary;
+        memcpy(w, logits + (size_t)r * rowStride + rowOffset, sizeof(float) * vocabulary);
+        for (int k = 0; k < n; k++) {
+            int id = (int)history[(size_t)r * capacity + (int)((len - 1 - (uint32_t)k) % (uint32_t)capacity)];
+            int seenMoreRecently = 0, count = 0;
+            for (int q = 0; q < n; q++) {
+                int other = (int)history[(size_t)r * capacity + (int)((len - 1 - (uint32_t)q) % (uint32_t)capacity)];
+                if (other == id) { count++; seenMoreRecently |= q < k; }
+            }
+            if (seenMoreRecently || (unsigned)id >= (unsigned)vocabulary) continue;
+            float x = w[id];
+            x = x > 0.0f ? x / repeat : x * repeat;
+            w[id] = x - presence - frequency * count;
+        }
+    }
+}
+
+/* HistoryPush, CpuBackend.Decoding.cs:284-292. */
+ORC_API void orc_history_push(const float *ids, float *history, const float *length, int rows, int capacity)
+{
+    uint32_t len = (uint32_t)length[0];
+    for (int r = 0; r < rows; r++) history[(size_t)r * capacity + (int)(len % (uint32_t)capacity)] = ids[r];
+}

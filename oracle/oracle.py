@@ -267,3 +267,34 @@ def max_err(expected, actual) -> float:
     e = np.asarray(expected, dtype=np.float64)
     a = np.asarray(actual, dtype=np.float64)
     return float(np.max(np.abs(e - a) / np.maximum(1.0, np.abs(e)))) if e.size else 0.0
+
+
+# ---------------------------------------------------------------- token sampler
+def sample_rows(logits, step: int, rows: int, vocabulary: int, row_stride: int, row_offset: int, temperature: float = 1.0,
+                top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, seed: int = 0, stats=None):
+    """Returns (ids [rows], stats [(step+1)*rows*13]) -- Backend.SampleRows (Backends/Backend.cs:248)."""
+    logits = _f32(logits)
+    ids = np.zeros(rows, dtype=np.float32)
+    if stats is None:
+        stats = np.zeros((step + 1) * rows * 13, dtype=np.float32)
+    st = np.array([step], dtype=np.float32)
+    lib().orc_sample_rows(_p(logits), _p(ids), _p(stats), _p(st), C.c_int(rows), C.c_int(vocabulary), C.c_int(row_stride), C.c_int(row_offset),
+                          C.c_float(temperature), C.c_int(top_k), C.c_float(top_p), C.c_float(min_p), C.c_uint32(seed))
+    return ids, stats
+
+
+def penalize_rows(logits, history, length: int, rows: int, vocabulary: int, row_stride: int, row_offset: int, capacity: int, last_n: int,
+                  repeat: float, presence: float, frequency: float) -> np.ndarray:
+    logits, history = _f32(logits), _f32(history)
+    work = np.zeros((rows, vocabulary), dtype=np.float32)
+    ln = np.array([length], dtype=np.float32)
+    lib().orc_penalize_rows(_p(logits), _p(work), _p(history), _p(ln), C.c_int(rows), C.c_int(vocabulary), C.c_int(row_stride), C.c_int(row_offset),
+                            C.c_int(capacity), C.c_int(last_n), C.c_float(repeat), C.c_float(presence), C.c_float(frequency))
+    return work
+
+
+def history_push(ids, history, length: int, capacity: int) -> None:
+    ids = _f32(ids)
+    assert history.dtype == np.float32 and history.flags["C_CONTIGUOUS"]
+    ln = np.array([length], dtype=np.float32)
+    lib().orc_history_push(_p(ids), _p(history), _p(ln), C.c_int(ids.size), C.c_int(capacity))
