@@ -290,6 +290,15 @@ NS_API int ns_linear_info(ns_linear_t linear, int* k_local, int* n_local, int* m
  * ns_layernorm with NS_I8 output).  NS_BF16 layer: x bf16, x_scale 0.  A row shard (tp_size > 1) takes NS_EPI_NONE only. */
 NS_API int ns_linear_forward(ns_device_t dev, ns_linear_t linear, uint64_t x, uint64_t x_scale, int M, int epilogue, uint64_t residual,
                              int residual_dtype, int out_dtype, uint64_t y);
+/* Host-to-host forward: y_host[M, N] = epilogue(x_host[M, K] . W^T), float32 in host memory on both sides (pinned memory
+ * for full speed).  Replaces the caller's sequence Tensor.From -> Linear.Forward -> Tensor.ToArray (Tensor.cs:87,204;
+ * Backend.Upload / Download, Backends/Backend.cs:77-79, CudaBackend.cs:283-301), whose three steps run one after another:
+ * here row chunks of `chunk_rows` (0 = about 32 MiB each, shorter at both ends) flow through an upload stream, the
+ * device's stream (quantise or convert, product) and a download stream, so both copy directions and the compute overlap,
+ * also between back-to-back calls.  x_host is read from the moment of the call; ns_stream_sync (or an event recorded
+ * after the call) covers the downloads into y_host.  epilogue: NS_EPI_NONE, NS_EPI_BIAS or NS_EPI_BIAS_GELU.  Not
+ * capturable; not for tensor-parallel shards. */
+NS_API int ns_linear_forward_host(ns_device_t dev, ns_linear_t linear, const float* x_host, int M, int epilogue, float* y_host, int chunk_rows);
 
 /* ------------------------------------------------------------------------------------------------
  * Tensor parallelism over NCCL.  No counterpart in the reference (single device; Device.cs:54-64).

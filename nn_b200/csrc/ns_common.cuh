@@ -53,6 +53,9 @@ struct NsDevice {
     int force_bn = 0;
     int force_splits = 0;
     int capturing = 0;
+    // streams, events and staging buffers of the host-to-host pipeline (ns_linear_forward_host); made on first use
+    void* host_pipe = nullptr;
+    void (*host_pipe_free)(void*) = nullptr;
     std::mutex lock;
 };
 

@@ -153,3 +153,25 @@ extern "C" int ns_linear_forward(ns_device_t h, ns_linear_t lh, uint64_t x, uint
     p.residual = reinterpret_cast<const void*>(residual);
     return ns_gemm_run(d, L->mode == NS_I8 ? NS_KIND_I8 : NS_KIND_BF16, reinterpret_cast<const void*>(x), L->w, false, M, L->N_loc, L->K_loc, p);
 }
+
+// Internal entry points for the host-to-host pipeline (ns_host_pipeline.cu).
+int ns_linear_shape(NsLinear* L, int* K, int* N, int* mode, int* split_ranks)
+{
+    NS_REQUIRE(L != nullptr, NS_ERR_ARGUMENT, "linear is null");
+    *K = L->K_loc; *N = L->N_loc; *mode = L->mode; *split_ranks = L->split == NS_SPLIT_NONE ? 1 : L->tp_size;
+    return NS_OK;
+}
+
+int ns_linear_forward_on(NsDevice* d, NsLinear* L, const void* x, const float* x_scale, int M, int epilogue, void* y)
+{
+    NS_REQUIRE(epilogue == NS_EPI_NONE || L->bias != nullptr, NS_ERR_ARGUMENT, "the layer has no bias for epilogue %d", epilogue);
+    NsGemmParams p = {};
+    p.epilogue = epilogue;
+    p.out_dtype = NS_F32;
+    p.residual_dtype = NS_F32;
+    p.out = y;
+    p.a_scale = x_scale;
+    p.w_scale = L->w_scale;
+    p.bias = epilogue == NS_EPI_NONE ? nullptr : L->bias;
+    return ns_gemm_run(d, L->mode == NS_I8 ? NS_KIND_I8 : NS_KIND_BF16, x, L->w, false, M, L->N_loc, L->K_loc, p);
+}

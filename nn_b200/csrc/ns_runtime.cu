@@ -115,6 +115,7 @@ extern "C" int ns_device_close(ns_device_t h)
     int rc = ns_device_make_current(d);
     if (rc != NS_OK) return rc;
     cudaStreamSynchronize(d->stream);
+    if (d->host_pipe && d->host_pipe_free) d->host_pipe_free(d->host_pipe);
     if (d->scratch) cudaFree(d->scratch);
     if (d->status_host) cudaFreeHost(d->status_host);
     if (d->owns_stream && d->stream) cudaStreamDestroy(d->stream);

@@ -50,6 +50,15 @@ class GptF32:
         self.next_ids = a(batch, True)
         self.length = 0
         self.graph = None
+        self.sampler = None                         # a TokenSampler replaces the greedy choice (CharGpt.cs:283-300)
+
+    def set_sampler(self, sampler) -> None:
+        """Sample with ``sampler`` (nn_b200.sampling.TokenSampler for this batch and vocabulary) instead of greedily.
+        A recorded step is dropped: the sampler's kernels become part of the next recording."""
+        self.sampler = sampler
+        if self.graph is not None:
+            self.be.DestroyGraph(self.graph)
+            self.graph = None
 
     # Linear.ForwardCore: product, then the bias as a second kernel (Layers/Linear.cs:43-47)
     def _linear(self, x, w, b, y, m, k, n):
@@ -103,7 +112,11 @@ class GptF32:
         be.LayerNormFused(x, w["lnf_g"], w["lnf_b"], self.h, m, D, cfg.eps)
         self._linear(self.h, w["head_w"], w["head_b"], self.logits, m, D, V)
         # greedy token of the last position (TokenSampler reads row r at r * rowStride + rowOffset, Sampling.cs:122)
-        be.ArgMaxRows(self.logits, self.next_ids, B, V, t * V, (t - 1) * V)
+        if self.sampler is None:
+            be.ArgMaxRows(self.logits, self.next_ids, B, V, t * V, (t - 1) * V)
+        else:
+            self.sampler.Sample(self.logits, t)
+            be.Copy(self.sampler.Ids, self.next_ids, B)
         be.Affine(self.position, self.position, 1, 1.0, float(t))                             # DecodingContext.EndStep
 
     def reset(self) -> None:

@@ -57,8 +57,8 @@ class TokenSampler:
 
     def Sample(self, logits: Storage, steps: int = 1) -> None:
         """Sampling.cs:111-138.  ``logits`` is [rows, vocabulary] or, with ``steps`` > 1, [rows, steps, vocabulary]
-        (the last position of each row is sampled)."""
-        if logits.count != self.Rows * steps * self.Vocabulary:
+        (the last position of each row is sampled); the storage may be larger than that."""
+        if logits.count < self.Rows * steps * self.Vocabulary:
             raise ValueError(f"Expected [{self.Rows}, ..., {self.Vocabulary}] logits, got {logits.count} values.")
         b = self._b
         rowStride, rowOffset = steps * self.Vocabulary, (steps - 1) * self.Vocabulary

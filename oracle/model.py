@@ -50,7 +50,8 @@ class _Generator:
     """The reference's generate loop (CharGpt.cs:261-308): prefill min(len, context-1) tokens, one cached step per
     token, and when the window is full re-read the last context/2 tokens from position 0."""
 
-    def generate(self, prompt, n_new: int):
+    def generate(self, prompt, n_new: int, sampler=None):
+        """``sampler``: an oracle.sampler.TokenSampler replacing the greedy choice (CharGpt.cs:283-300)."""
         cfg = self.cfg
         history = [list(map(int, row)) for row in np.asarray(prompt)]
         out = [[] for _ in history]
@@ -61,7 +62,7 @@ class _Generator:
             return np.array([h[-keep:] for h in history], dtype=np.int64)
 
         def take(logits):
-            ids = orc.argmax(logits).astype(np.int64)
+            ids = orc.argmax(logits).astype(np.int64) if sampler is None else sampler.sample(logits)
             self.logit_trace.append(logits.copy())
             for b, t in enumerate(ids):
                 history[b].append(int(t)); out[b].append(int(t))

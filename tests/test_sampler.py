@@ -254,3 +254,39 @@ def test_device_sampler_in_graph(backend, dev, orc):
     direct, replayed = run(False), run(True)
     assert direct == replayed
     assert any(direct[i] != direct[i + 1] for i in range(steps - 1)), "penalties and the step counter must change the draws"
+
+
+@pytest.mark.gpu
+def test_generate_with_sampler(backend, dev, orc):
+    """CharGpt.Generate with a TokenSampler in the recorded step (CharGpt.cs:261-308): prefill samples from the last
+    of several positions, the graph replays the sampling kernels, a context reset samples again from a prefill."""
+    from nn_b200.gpt import GptConfig
+    from nn_b200.gpt_f32 import GptF32
+    from nn_b200.sampling import TokenSampler
+    from oracle import model as om
+    from oracle.sampler import TokenSampler as OracleSampler
+    cfg = GptConfig(vocab=40, dim=32, heads=2, layers=2, ff_dim=128, context=24)
+    w = om.make_weights(cfg, seed=21, std=0.3, sinusoid=True)
+    B, n_new = 3, 30
+    prompt = orc.token_ids((B, 5), 8, cfg.vocab).astype(np.int64)
+    o = OracleSampler(B, cfg.vocab, n_new)
+    o.temperature, o.top_k, o.top_p, o.repeat, o.seed = 0.7, 12, 0.95, 1.15, 77
+    o.set_history([int(t) for t in prompt[0]])
+    ref = om.F32Decoder(cfg, w, B)
+    exp, exp_resets = ref.generate(prompt, n_new, sampler=o)
+    m = GptF32(dev, cfg, w, B, max_steps=12)
+    s = TokenSampler(m.be, B, cfg.vocab, n_new)
+    s.Temperature, s.TopK, s.TopP, s.RepeatPenalty, s.Seed = 0.7, 12, 0.95, 1.15, 77
+    s.SetHistory([int(t) for t in prompt[0]])
+    m.set_sampler(s)
+    got, resets, trace = m.generate(prompt, n_new, use_graph=True)
+    assert resets == exp_resets >= 1
+    # identical up to the first draw that differs (a rounding-level difference at a boundary of the running sum)
+    same = 0
+    while same < n_new and np.array_equal(got[:, same], exp[:, same]):
+        assert orc.close(ref.logit_trace[same], trace[same], 1e-4)
+        same += 1
+    assert same >= n_new // 2, f"draws diverge at step {same}"
+    stats = s.Read(0, n_new)
+    assert [[t.Id for t in row] for row in stats] == [list(got[:, i]) for i in range(n_new)]
+    assert all(0.0 < t.Probability <= 1.0 and t.Entropy >= 0.0 for row in stats for t in row)
