@@ -76,7 +76,8 @@ NS_API int ns_device_stream(ns_device_t dev, uint64_t* stream);
 NS_API int ns_stream_sync(ns_device_t dev);
 /* Reads and clears the device status word: 0 = no kernel gave up a wait. */
 NS_API int ns_device_status(ns_device_t dev, int* status);
-/* Tuning overrides for experiments: tile width (0, 32, 64, 128, 256) and split-K count (0 = heuristic). */
+/* Tuning overrides for experiments: tile width (0, 32, 64, 128, 256; 512 = the CTA-pair kernel where a shape allows it,
+ * 256 = never the pair kernel) and split-K count (0 = heuristic). */
 NS_API int ns_device_tune(ns_device_t dev, int tile_n, int k_splits);
 
 /* ------------------------------------------------------------------------------------------------

@@ -479,6 +479,241 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair kernel for large products (weights stored [N, K], no K split).
+//
+// With one CTA per 128 x 256 tile every k-block needs 48 KB from L2 (16 KB of A, 32 KB of B) for 512 tensor-core
+// cycles of int8 (or bf16) work, and an SM takes in about 64 bytes per cycle: 768 cycles of loading per 512 cycles
+// of math.  Measured: 128 x 128 tiles (32 KB per k-block for half the math) take 65 % of the time of 128 x 256
+// tiles, not 50 %: the loop runs at the speed of the loads.  Here two CTAs of a cluster work on one 256 x 256
+// tile: each loads its own 128 rows of A and HALF of the B tile (128 of its 256 rows), 32 KB per k-block, and the
+// even CTA's MMA thread issues tcgen05.mma.cta_group::2, which multiplies the pair's 256 rows of A with all 256
+// rows of B, reading each half of B from the shared memory of the CTA that loaded it.  Each CTA ends up with its
+// own 128 x 256 accumulator in its own tensor memory and runs the same epilogue as the single-CTA kernel.
+//
+// Barriers: full[s] lives in the even CTA and counts the bytes of both CTAs' loads (each TMA names the even CTA's
+// barrier); empty[s] and acc_full[a] exist in both CTAs and are signalled by a tcgen05.commit that arrives in both;
+// acc_empty[a] lives in the even CTA and is arrived on by the 8 epilogue warps of the pair (the odd CTA's remotely).
+// The two CTAs synchronise as a cluster after setting up barriers and before freeing tensor memory, so neither
+// touches the other's shared memory outside that window.
+struct PairCfg {
+    static constexpr int BN = 256;                 // columns of the pair's tile
+    static constexpr int BN_HALF = 128;            // rows of B one CTA loads
+    static constexpr int STAGES = 6;
+    static constexpr uint32_t A_BYTES = BM * BKB;
+    static constexpr uint32_t B_BYTES = BN_HALF * BKB;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t TMEM_COLS = 2 * BN;
+    static constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 256;
+};
+
+// p.tiles_m / p.tiles_n count 256 x 256 tiles here.  Groups of 8 tile rows, rows fastest: the clusters running at
+// the same time share A rows and B columns in L2.
+__device__ __forceinline__ void pair_coords(const NsGemmParams& p, int item, int& tm, int& tn)
+{
+    const int group_rows = 8;
+    const int per_group = group_rows * p.tiles_n;
+    const int g = item / per_group;
+    const int r = item - g * per_group;
+    const int rows_here = min(group_rows, p.tiles_m - g * group_rows);
+    tm = g * group_rows + r % rows_here;
+    tn = r / rows_here;
+}
+
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ StoreMaps sm, const NsGemmParams p)
+{
+    using Cfg = PairCfg;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr int BN = Cfg::BN;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int abort_flag_storage;
+    volatile int* abort_flag = &abort_flag_storage;
+
+    const uint32_t smem_base = (ns_smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t epi_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t bar_base = epi_base + EPI_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ns_cluster_ctarank();        // 0: issues the MMAs
+    const int cluster = blockIdx.x >> 1;
+    const int n_clusters = gridDim.x >> 1;
+    const int n_items = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        abort_flag_storage = 0;
+        for (int s = 0; s < STAGES; s++) {
+            ns_mbar_init(full_bar(s), 1);
+            ns_mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            ns_mbar_init(tfull_bar(a), 1);
+            ns_mbar_init(tempty_bar(a), 8);            // 4 epilogue warps of each CTA
+        }
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(tmem_slot), "r"(0xFFFFFFFFu) : "memory");
+        ns_fence_barrier_init();
+        ns_fence_proxy_async();
+        ns_prefetch_tensormap(&tmA);
+        ns_prefetch_tensormap(&tmB);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        ns_tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+        ns_tmem_relinquish_pair();
+    }
+    ns_tc_fence_before();
+    ns_cluster_sync();                                 // both CTAs' barriers exist before anything remote happens
+    ns_tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+    if (tmem_base == 0xFFFFFFFFu) tmem_base = ns_ld_shared_cluster_u32(ns_mapa(tmem_slot, rank ^ 1u));
+
+    constexpr int ELEMS_PER_KB = KIND == NS_KIND_I8 ? 128 : 64;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer (both CTAs)
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int item = cluster; item < n_items && ok; item += n_clusters) {
+                int tm, tn;
+                pair_coords(p, item, tm, tn);
+                const int row0 = tm * 256 + (int)rank * BM;
+                const int brow0 = tn * BN + (int)rank * Cfg::BN_HALF;
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    ok = ns_mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, p.status_base + 11);
+                    if (!ok) break;
+                    // the even CTA's barrier counts the four boxes of the pair (boxes that reach past the matrix
+                    // edge are zero-filled and still count in full)
+                    if (rank == 0) ns_mbar_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
+                    const uint32_t bar = ns_mapa(full_bar(s), 0);
+                    const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
+                    ns_tma_load_2d_pair(a_dst, &tmA, bar, kb * ELEMS_PER_KB, row0);
+                    ns_tma_load_2d_pair(a_dst + Cfg::A_BYTES, &tmB, bar, kb * ELEMS_PER_KB, brow0);
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+            }
+            // the commits that free the last ring slots arrive in this CTA's shared memory: see them land before leaving
+            for (int i = 0; i < STAGES && ok; i++) {
+                ok = ns_mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, p.status_base + 15);
+                if (++s == STAGES) { s = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (even CTA only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = KIND == NS_KIND_I8 ? ns_idesc(2, 1, 0, 0, 256, BN) : ns_idesc(1, 1, 0, 0, 256, BN);
+            const uint64_t desc_k = ns_desc_base(16, 1024);
+            int s = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int item = cluster; item < n_items && ok; item += n_clusters, local++) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                ok = ns_mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, p.status_base + 12);
+                if (!ok) break;
+                ns_tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    ok = ns_mbar_wait(full_bar(s), phase, abort_flag, p.status, p.status_base + 13);
+                    if (!ok) break;
+                    ns_tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * Cfg::STAGE_BYTES;
+                    const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < 4; kk++) {
+                        const uint64_t a_desc = ns_desc_at(desc_k, a_addr + kk * 32);
+                        const uint64_t b_desc = ns_desc_at(desc_k, b_addr + kk * 32);
+                        const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+                        if (KIND == NS_KIND_I8) ns_mma_i8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+                        else ns_mma_f16_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+                    }
+                    ns_tc_commit_pair(empty_bar(s), 3);       // the ring slot is free in both CTAs
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+                if (ok) ns_tc_commit_pair(tfull_bar(acc), 3);   // both CTAs' epilogues may read their accumulator
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+        const int quad = warp & 3;
+        EpiCtx cx;
+        cx.lane = lane;
+        cx.bufs = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
+        cx.nbuf = 0;
+        cx.split = 0;
+        int local = 0;
+        bool ok = true;
+        const uint32_t tempty_even0 = ns_mapa(tempty_bar(0), 0), tempty_even1 = ns_mapa(tempty_bar(1), 0);
+        for (int item = cluster; item < n_items && ok; item += n_clusters, local++) {
+            int tm, tn;
+            pair_coords(p, item, tm, tn);
+            const int acc = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            cx.row0 = tm * 256 + (int)rank * BM + quad * 32;
+            cx.row = cx.row0 + lane;
+            cx.row_ok = cx.row < p.M;
+            cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok) ? __ldg(&p.a_scale[cx.row]) : 1.0f;
+            if (warp == 2) {
+                const int pc = tn * BN + (lane & 7) * 32;
+                if (lane < BN / 32 && pc < p.N) {
+                    if (KIND == NS_KIND_I8) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.w_scale + pc));
+                    if (p.epilogue != NS_EPI_NONE) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.bias + pc));
+                }
+            }
+            ok = ns_mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, p.status_base + 14);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ns_tc_fence_after();
+            const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
+            const bool warp_has_rows = cx.row0 < p.M;
+            uint32_t ra[32], rb[32];
+            __syncwarp();
+            ns_tmem_ld32(t_row, ra);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c += 2) {
+                ns_tc_wait_ld();
+                __syncwarp();
+                ns_tmem_ld32(t_row + (c + 1) * 32, rb);
+                if (warp_has_rows && tn * BN + c * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, ra, tn * BN + c * 32);
+                ns_tc_wait_ld();
+                __syncwarp();
+                if (c + 2 < BN / 32) ns_tmem_ld32(t_row + (c + 2) * 32, ra);
+                if (warp_has_rows && tn * BN + (c + 1) * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, rb, tn * BN + (c + 1) * 32);
+            }
+            ns_tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ns_mbar_arrive_cluster(acc ? tempty_even1 : tempty_even0);
+        }
+        if (lane == 0) ns_bulk_wait_read<0>();
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ns_tc_fence_before();
+    __syncthreads();
+    if (*abort_flag != 0 && threadIdx.x == 0) {
+        long long t0 = clock64();
+        while (clock64() - t0 < 400000) { }
+    }
+    // neither CTA may leave (or free tensor memory) while the other's MMAs, loads or arrivals can still reach it
+    ns_cluster_sync();
+    if (warp == 1) {
+        ns_tc_fence_after();
+        ns_tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
 // Sums split-K partials in split order and applies the epilogue.  One thread per 4 columns.
 template <int KIND>
 __global__ void ns_gemm_splitk_finish_kernel(const NsGemmParams p)
@@ -548,6 +783,34 @@ int launch_gemm(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, con
     return NS_OK;
 }
 
+template <int KIND>
+int launch_pair(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p)
+{
+    auto kernel = ns_gemm_pair_kernel<KIND>;
+    static int max_clusters[64] = {0};
+    if (max_clusters[d->ordinal] == 0) {
+        NS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg::SMEM_BYTES));
+        // how many pairs the device can hold at once (a GPC with an odd number of free SMs leaves one unpaired)
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(d->sm_count & ~1);
+        q.blockDim = dim3(GEMM_THREADS);
+        q.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        q.attrs = attr;
+        q.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n <= 0) { cudaGetLastError(); n = d->sm_count / 2; }
+        if (n > d->sm_count / 2) n = d->sm_count / 2;
+        max_clusters[d->ordinal] = n;
+    }
+    const int items = p.tiles_m * p.tiles_n;
+    const int clusters = items < max_clusters[d->ordinal] ? items : max_clusters[d->ordinal];
+    NS_CUDA(ns_launch_plain(kernel, dim3(2 * clusters), dim3(GEMM_THREADS), PairCfg::SMEM_BYTES, d->stream, tmA, tmB, sm, p));
+    return NS_OK;
+}
+
 template <int KIND, bool B_MN>
 int dispatch_bn(NsDevice* d, int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p)
 {
@@ -570,7 +833,7 @@ void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* b
     const int tiles_m = (M + BM - 1) / BM;
     int bn = 256;
     if (d->force_bn) {
-        bn = d->force_bn == 32 ? 64 : d->force_bn;
+        bn = d->force_bn == 32 ? 64 : (d->force_bn == 512 ? 256 : d->force_bn);
     } else if (tiles_m == 1) {
         bn = b_is_kn ? 256 : 128;
         while (bn > 64 && bn / 2 >= N) bn >>= 1;
@@ -607,9 +870,13 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     p.k_blocks = (int)(((int64_t)K * elsize + BKB - 1) / BKB);
     int bn, splits;
     ns_gemm_choose_tiling(d, M, N, p.k_blocks, &bn, &splits, b_is_kn);
+    // Large products with [N, K] weights go to the CTA-pair kernel (256 x 256 tiles over two SMs): whenever 256-wide
+    // tiles without a K split were chosen and there are at least two row tiles.  Tuning override 512 forces it, 256
+    // forces the single-CTA kernel.
+    const bool pair = !b_is_kn && splits == 1 && M > BM && (d->force_bn == 512 || (d->force_bn == 0 && bn == 256));
     p.kb_per_split = (p.k_blocks + splits - 1) / splits;
     p.k_splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
-    p.tiles_m = (M + BM - 1) / BM;
+    p.tiles_m = pair ? (M + 255) / 256 : (M + BM - 1) / BM;
     p.tiles_n = (N + bn - 1) / bn;
     p.status = d->status_dev;
     p.status_base = kind == NS_KIND_I8 ? 100 : 200;
@@ -643,7 +910,7 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     if (!b_is_kn) {
         uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
         uint64_t strides[1] = {(uint64_t)K * elsize};
-        uint32_t box[2] = {box_k, (uint32_t)bn};
+        uint32_t box[2] = {box_k, (uint32_t)(pair ? PairCfg::BN_HALF : bn)};
         rc = ns_make_tensor_map(&tmB, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != NS_OK) return rc;
     } else {
@@ -689,7 +956,8 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
             }
         }
     }
-    if (kind == NS_KIND_I8) rc = dispatch_bn<NS_KIND_I8, false>(d, bn, tmA, tmB, sm, p);
+    if (pair) rc = kind == NS_KIND_I8 ? launch_pair<NS_KIND_I8>(d, tmA, tmB, sm, p) : launch_pair<NS_KIND_BF16>(d, tmA, tmB, sm, p);
+    else if (kind == NS_KIND_I8) rc = dispatch_bn<NS_KIND_I8, false>(d, bn, tmA, tmB, sm, p);
     else if (!b_is_kn) rc = dispatch_bn<NS_KIND_BF16, false>(d, bn, tmA, tmB, sm, p);
     else rc = dispatch_bn<NS_KIND_BF16, true>(d, bn, tmA, tmB, sm, p);
     if (rc != NS_OK) return rc;

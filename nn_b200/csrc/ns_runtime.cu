@@ -174,8 +174,8 @@ extern "C" int ns_device_tune(ns_device_t h, int tile_n, int k_splits)
 {
     NsDevice* d = ns_dev(h);
     NS_REQUIRE(d != nullptr, NS_ERR_ARGUMENT, "ns_device_tune: device is null");
-    NS_REQUIRE(tile_n == 0 || tile_n == 32 || tile_n == 64 || tile_n == 128 || tile_n == 256, NS_ERR_ARGUMENT,
-               "ns_device_tune: tile_n must be 0, 32, 64, 128 or 256");
+    NS_REQUIRE(tile_n == 0 || tile_n == 32 || tile_n == 64 || tile_n == 128 || tile_n == 256 || tile_n == 512, NS_ERR_ARGUMENT,
+               "ns_device_tune: tile_n must be 0, 32, 64, 128, 256 or 512");
     NS_REQUIRE(k_splits >= 0 && k_splits <= 64, NS_ERR_ARGUMENT, "ns_device_tune: k_splits must be in [0, 64]");
     d->force_bn = tile_n;
     d->force_splits = k_splits;

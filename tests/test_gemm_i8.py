@@ -129,3 +129,24 @@ def test_argument_errors(dev):
         N.call("ns_qmatmul_i8", dev.handle, a.ptr, s.ptr, a.ptr, s.ptr, 0, 0, 0, 2, 2, 24, 0, 0, s.ptr, 0)
     with pytest.raises(N.NsError):  # bias epilogue without a bias
         N.call("ns_qmatmul_i8", dev.handle, a.ptr, s.ptr, a.ptr, s.ptr, 0, 0, 0, 2, 2, 16, N.EPI_BIAS, 0, s.ptr, 0)
+
+
+@pytest.mark.parametrize("M,Nn,K", [(256, 256, 128), (129, 520, 4096), (300, 1000, 256), (700, 264, 1040), (1024, 768, 2048)])
+@pytest.mark.parametrize("epi", [N.EPI_BIAS, N.EPI_BIAS_RESIDUAL])
+def test_cta_pair_kernel_bit_exact(dev, orc, M, Nn, K, epi):
+    """The two-CTA kernel (256 x 256 tiles, tcgen05 cta_group::2), forced onto shapes small enough for the oracle:
+    full tiles, ragged rows (second CTA partly or wholly past M), ragged columns, many k-blocks (the 6-stage ring
+    wraps), several tiles per cluster (both accumulators in use)."""
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=13)
+    res = orc.normal((M, Nn), 77) if epi == N.EPI_BIAS_RESIDUAL else None
+    dev.tune(512, 1)
+    try:
+        y, raw = _run(dev, aq, a_s, wq, w_s, bias, residual=res, epilogue=epi)
+        yb, _ = _run(dev, aq, a_s, wq, w_s, bias, residual=res, epilogue=epi, out_dtype=N.NS_BF16, want_raw=False)
+    finally:
+        dev.tune(0, 0)
+    acc = orc.qmatmul_i8_acc(aq, wq)
+    assert np.array_equal(raw, acc), f"accumulators differ at {np.argwhere(raw != acc)[:4]}"
+    exp = orc.dequant_epilogue(acc, a_s, w_s, bias, residual=res)
+    assert np.array_equal(y.view(np.uint32), exp.view(np.uint32)), f"max err {orc.max_err(exp, y)}"
+    assert np.array_equal(yb, orc.round_bf16(exp))
