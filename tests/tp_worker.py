@@ -69,8 +69,17 @@ def gpu_mode():
     ref0 = mine.clone()
     td.broadcast(ref0, 0)
     assert torch.equal(mine, ref0)
+    # Greedy tokens equal the oracle's up to the first step where the oracle's two best logits are closer than the
+    # logit tolerance (a near-tie may flip, and the sequences differ from there on): check every sequence up to that
+    # step and that the step really is a near-tie.
     agree = float((got == exp).mean())
-    assert agree > 0.9, f"token agreement with the oracle {agree}"
+    for b in range(B):
+        diff = np.nonzero(got[b] != exp[b])[0]
+        if diff.size:
+            s = int(diff[0])
+            top2 = np.sort(ref.logit_trace[s][b])[-2:]
+            assert top2[1] - top2[0] <= 2 * 5e-2 * max(1.0, abs(float(top2[1]))), \
+                f"sequence {b} leaves the oracle's tokens at step {s} without a near-tie (gap {top2[1] - top2[0]:.3g})"
     m.close()
     dist.barrier()
     print(f"rank {rank}: gpu ok, agreement {agree:.3f}")
