@@ -244,11 +244,14 @@ def run_ours(args, rank, world, local_rank):
             dist.destroy_process_group()
         return
     achieved = OPS / (ms_step * 1e-3) / 1e12
-    int8_peak = 2.0 * peaks["bf16"]
+    # The timed steps run inside about a second of back-to-back products (the clocks window), under the power cap:
+    # the sustained figure is the denominator; the burst one and the nominal one are given beside it.
+    int8_peak = 2.0 * peaks["bf16_sustained"]
     roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s", "frac": achieved / int8_peak,
-                "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "ns_gemm_tc_kernel<int8, 256>",
-                "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); that file has no int8 figure; "
-                               "nominal dense int8 is 4500", "frac_of_nominal_4500": achieved / 4500.0,
+                "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "ns_gemm_pair_kernel<int8> (256 x 256 tiles, tcgen05 cta_group::2)",
+                "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}; a kernel timed inside a long "
+                               "loaded region, SM clock in `clocks`); that file has no int8 figure; nominal dense int8 is 4500",
+                "frac_of_burst": achieved / (2.0 * peaks["bf16"]), "frac_of_nominal_4500": achieved / 4500.0,
                 "algorithmic_bytes": ALGO_BYTES, "hbm_gbs_at_this_rate": ALGO_BYTES / (ms_step * 1e-3) / 1e9}
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i8",
@@ -265,7 +268,7 @@ def run_ours(args, rank, world, local_rank):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
 # in profiles/.
-TRAFFIC_BYTES_PER_LAUNCH = 145327360  # 63.33 MB read + 82.00 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
+TRAFFIC_BYTES_PER_LAUNCH = 145519104  # 62.24 MB read + 83.28 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
 
 
 def run_case(spec: str):
