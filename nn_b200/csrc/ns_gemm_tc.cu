@@ -126,9 +126,12 @@ __device__ __forceinline__ void add_residual32(const NsGemmParams& p, size_t bas
 // written again the store that last read it must have finished reading (wait_group.read 1).
 template <int WORDS>
 __device__ __forceinline__ void stage_and_store(uint32_t buf, int lane, const uint32_t (&w)[32], const CUtensorMap* map, int x, int y, int z,
-                                                bool three_d)
+                                                bool three_d, bool single = false)
 {
-    if (lane == 0) ns_bulk_wait_read<1>();
+    if (lane == 0) {
+        if (single) ns_bulk_wait_read<0>();
+        else ns_bulk_wait_read<1>();
+    }
     __syncwarp();
 #pragma unroll
     for (int q = 0; q < WORDS / 4; q++) {
@@ -149,8 +152,9 @@ struct EpiCtx {
     int lane, row0, row, split;
     bool row_ok;
     float a_scale;
-    uint32_t bufs;   // two staging buffers
+    uint32_t bufs;   // two staging buffers (one when `single`)
     int nbuf;        // stores queued so far (selects the buffer)
+    bool single;     // one staging buffer: a second warp on the same scheduler covers the wait for its store
 };
 
 // Finishes 32 columns [col0, col0+32) of this thread's row from accumulator words r and sends them out.
@@ -162,7 +166,7 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
     const size_t base = (size_t)cx.row * p.N + col0;
     if (p.k_splits > 1) {
         if (p.tma_store) {
-            stage_and_store<32>(cx.bufs + (cx.nbuf & 1) * EPI_BUF_BYTES, cx.lane, r, &sm.part, col0, cx.row0, cx.split, true);
+            stage_and_store<32>(cx.bufs + (cx.single ? 0 : (cx.nbuf & 1)) * EPI_BUF_BYTES, cx.lane, r, &sm.part, col0, cx.row0, cx.split, true, cx.single);
             cx.nbuf++;
         } else if (cx.row_ok) {
             uint32_t* dst = reinterpret_cast<uint32_t*>(p.partial) + (size_t)cx.split * p.M * p.N + base;
@@ -174,7 +178,7 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
     }
     if (KIND == NS_KIND_I8 && p.raw != nullptr) {
         if (p.tma_store) {
-            stage_and_store<32>(cx.bufs + (cx.nbuf & 1) * EPI_BUF_BYTES, cx.lane, r, &sm.raw, col0, cx.row0, 0, false);
+            stage_and_store<32>(cx.bufs + (cx.single ? 0 : (cx.nbuf & 1)) * EPI_BUF_BYTES, cx.lane, r, &sm.raw, col0, cx.row0, 0, false, cx.single);
             cx.nbuf++;
         } else if (cx.row_ok) {
 #pragma unroll
@@ -231,7 +235,7 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
             uint32_t w[32];
 #pragma unroll
             for (int j = 0; j < 32; j++) w[j] = __float_as_uint(v[j]);
-            stage_and_store<32>(cx.bufs + (cx.nbuf & 1) * EPI_BUF_BYTES, cx.lane, w, &sm.out, col0, cx.row0, 0, false);
+            stage_and_store<32>(cx.bufs + (cx.single ? 0 : (cx.nbuf & 1)) * EPI_BUF_BYTES, cx.lane, w, &sm.out, col0, cx.row0, 0, false, cx.single);
             cx.nbuf++;
         } else if (cx.row_ok) {
             float* dst = reinterpret_cast<float*>(p.out) + base;
@@ -245,7 +249,7 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
 #pragma unroll
             for (int j = 0; j < 16; j++)
                 w[j] = ns_f32_to_bf16_bits(v[2 * j]) | (uint32_t(ns_f32_to_bf16_bits(v[2 * j + 1])) << 16);
-            stage_and_store<16>(cx.bufs + (cx.nbuf & 1) * EPI_BUF_BYTES, cx.lane, w, &sm.out, col0, cx.row0, 0, false);
+            stage_and_store<16>(cx.bufs + (cx.single ? 0 : (cx.nbuf & 1)) * EPI_BUF_BYTES, cx.lane, w, &sm.out, col0, cx.row0, 0, false, cx.single);
             cx.nbuf++;
         } else if (cx.row_ok) {
             uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + base;
@@ -409,6 +413,7 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         cx.lane = lane;
         cx.bufs = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
         cx.nbuf = 0;
+        cx.single = false;
         int local = 0;
         bool ok = true;
         ns_pdl_wait();   // a_scale, residual and every output buffer belong to the previous kernel until it is done
@@ -520,8 +525,10 @@ __device__ __forceinline__ void pair_coords(const NsGemmParams& p, int item, int
     tn = r / rows_here;
 }
 
+constexpr int PAIR_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
+
 template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ StoreMaps sm, const NsGemmParams p)
 {
@@ -556,7 +563,7 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         for (int a = 0; a < 2; a++) {
             ns_mbar_init(tfull_bar(a), 1);
-            ns_mbar_init(tempty_bar(a), 8);            // 4 epilogue warps of each CTA
+            ns_mbar_init(tempty_bar(a), 16);           // 8 epilogue warps of each CTA
         }
         asm volatile("st.shared.b32 [%0], %1;" ::"r"(tmem_slot), "r"(0xFFFFFFFFu) : "memory");
         ns_fence_barrier_init();
@@ -646,11 +653,17 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
     } else {
         // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+        // Eight warps: two per tensor-memory lane quadrant (a warp reads the lanes of quadrant warp % 4), each taking one
+        // half of the 256 columns, so every scheduler has a second warp to issue while the first waits on tensor memory,
+        // on its column vectors or on its store.
         const int quad = warp & 3;
+        const int c_begin = ((warp - 2) >> 2) * (BN / 64);
+        const int c_end = c_begin + BN / 64;
         EpiCtx cx;
         cx.lane = lane;
-        cx.bufs = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
+        cx.bufs = epi_base + (warp - 2) * EPI_BUF_BYTES;
         cx.nbuf = 0;
+        cx.single = true;
         cx.split = 0;
         int local = 0;
         bool ok = true;
@@ -679,16 +692,16 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const bool warp_has_rows = cx.row0 < p.M;
             uint32_t ra[32], rb[32];
             __syncwarp();
-            ns_tmem_ld32(t_row, ra);
+            ns_tmem_ld32(t_row + c_begin * 32, ra);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c += 2) {
+            for (int c = c_begin; c < c_end; c += 2) {
                 ns_tc_wait_ld();
                 __syncwarp();
                 ns_tmem_ld32(t_row + (c + 1) * 32, rb);
                 if (warp_has_rows && tn * BN + c * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, ra, tn * BN + c * 32);
                 ns_tc_wait_ld();
                 __syncwarp();
-                if (c + 2 < BN / 32) ns_tmem_ld32(t_row + (c + 2) * 32, ra);
+                if (c + 2 < c_end) ns_tmem_ld32(t_row + (c + 2) * 32, ra);
                 if (warp_has_rows && tn * BN + (c + 1) * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, rb, tn * BN + (c + 1) * 32);
             }
             ns_tc_fence_before();
@@ -793,7 +806,7 @@ int launch_pair(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, con
         // how many pairs the device can hold at once (a GPC with an odd number of free SMs leaves one unpaired)
         cudaLaunchConfig_t q = {};
         q.gridDim = dim3(d->sm_count & ~1);
-        q.blockDim = dim3(GEMM_THREADS);
+        q.blockDim = dim3(PAIR_THREADS);
         q.dynamicSmemBytes = PairCfg::SMEM_BYTES;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -807,7 +820,7 @@ int launch_pair(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, con
     }
     const int items = p.tiles_m * p.tiles_n;
     const int clusters = items < max_clusters[d->ordinal] ? items : max_clusters[d->ordinal];
-    NS_CUDA(ns_launch_plain(kernel, dim3(2 * clusters), dim3(GEMM_THREADS), PairCfg::SMEM_BYTES, d->stream, tmA, tmB, sm, p));
+    NS_CUDA(ns_launch_plain(kernel, dim3(2 * clusters), dim3(PAIR_THREADS), PairCfg::SMEM_BYTES, d->stream, tmA, tmB, sm, p));
     return NS_OK;
 }
 
