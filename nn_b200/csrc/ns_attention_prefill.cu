@@ -47,6 +47,20 @@ struct FaMaps {
     CUtensorMap o;        // box [64 dims, 32 rows] (one softmax warp's rows)
 };
 
+__device__ __forceinline__ float fa_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// bf16(lo) in the low half, bf16(hi) in the high half, both round to nearest even: one instruction
+__device__ __forceinline__ uint32_t fa_pack_bf16(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
 enum { BAR_Q = 0, BAR_K0 = 1, BAR_V0 = 3, BAR_KV_EMPTY0 = 5, BAR_S_FULL0 = 7, BAR_S_FREE0 = 9, BAR_P_FULL = 11, BAR_PV_DONE = 12, BAR_PAIR0 = 13, BAR_COUNT = 17 };
 
 __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(const __grid_constant__ FaMaps maps, const FaParams p)
@@ -251,13 +265,14 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
             uint32_t pk[32];
 #pragma unroll
             for (int c = 0; c < 64; c += 4) {
-                const float p0 = exp2f(fmaf(__uint_as_float(sbits[c]), p.scale_log2, neg_m));
-                const float p1 = exp2f(fmaf(__uint_as_float(sbits[c + 1]), p.scale_log2, neg_m));
-                const float p2 = exp2f(fmaf(__uint_as_float(sbits[c + 2]), p.scale_log2, neg_m));
-                const float p3 = exp2f(fmaf(__uint_as_float(sbits[c + 3]), p.scale_log2, neg_m));
+                // one MUFU each (results below 2^-126 flush to zero, which is what P wants) and one conversion per pair
+                const float p0 = fa_exp2(fmaf(__uint_as_float(sbits[c]), p.scale_log2, neg_m));
+                const float p1 = fa_exp2(fmaf(__uint_as_float(sbits[c + 1]), p.scale_log2, neg_m));
+                const float p2 = fa_exp2(fmaf(__uint_as_float(sbits[c + 2]), p.scale_log2, neg_m));
+                const float p3 = fa_exp2(fmaf(__uint_as_float(sbits[c + 3]), p.scale_log2, neg_m));
                 s4[0] += p0; s4[1] += p1; s4[2] += p2; s4[3] += p3;
-                pk[c >> 1] = ns_f32_to_bf16_bits(p0) | (uint32_t(ns_f32_to_bf16_bits(p1)) << 16);
-                pk[(c >> 1) + 1] = ns_f32_to_bf16_bits(p2) | (uint32_t(ns_f32_to_bf16_bits(p3)) << 16);
+                pk[c >> 1] = fa_pack_bf16(p0, p1);
+                pk[(c >> 1) + 1] = fa_pack_bf16(p2, p3);
             }
             l_run = l_run * alpha + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
             // P and O belong to the previous P.V until it has completed
