@@ -14,14 +14,17 @@
 //   warp 0      one lane issues TMA loads: Q once, then K_j and V_j (128 keys each) into a 2-stage ring
 //   warp 1      one lane issues the MMAs: S_{j+1} = Q.K_{j+1}^T is issued before P_j.V_j, so the tensor
 //               cores work on the next scores while the softmax warps handle block j
-//   warps 2..9  softmax, two warps per accumulator quadrant (64 key columns each): thread r owns half of query row r
-//               (= tensor-memory lane r): reads its 64 scores with
-//               tcgen05.ld, masks, updates max/sum, writes P_j as bf16 into shared memory in the
-//               128-byte-swizzled K-major layout the MMA reads, rescales O in tensor memory when the
-//               row maximum grew by more than 2^8 (otherwise the old reference maximum is kept, which
-//               is exact because the sum and O share it), and at the end divides by the sum and stores
-//               O through shared memory with TMA stores.
-// Tensor memory: S0 at columns [0,128), S1 at [128,256), O at [256,384).
+//   warps 2..9  softmax, in two groups of four warps.  Group g owns the key blocks of parity g with its own score
+//               buffer, P buffer, output accumulator O_g and running (maximum, sum): thread r owns query row r
+//               (= tensor-memory lane r), reads its 128 scores with tcgen05.ld, masks, updates max/sum, writes P_j as
+//               bf16 into shared memory in the 128-byte-swizzled K-major layout the MMA reads, and rescales O_g in
+//               tensor memory when the row maximum grew by more than 2^8 (otherwise the old reference maximum is
+//               kept, which is exact because the sum and O_g share it).  The groups never wait for each other inside
+//               the loop, and the two warps on one scheduler are in different phases of their blocks, so one keeps
+//               the exponential unit busy while the other waits on tensor memory or writes P.  After the last block
+//               the two partial results of a row are merged (weights exp2(m_g - m) / l), and each group stores 64 of
+//               the 128 output dims through shared memory with TMA stores.
+// Tensor memory: S_0 at columns [0,128), S_1 at [128,256), O_0 at [256,384), O_1 at [384,512).
 // Every mbarrier wait is bounded; a wait that runs out reports a status code and the CTA leaves.
 #include <math.h>
 
@@ -33,7 +36,7 @@ constexpr int FA_THREADS = 320;  // producer warp, MMA warp, 8 softmax warps
 constexpr int FA_BLOCK = 128;  // query rows per CTA = keys per block = head_dim
 constexpr uint32_t FA_TILE_BYTES = 128 * 128 * 2;  // 32 KB: two [128 x 64] halves of 16 KB
 constexpr uint32_t FA_HALF_BYTES = 128 * 64 * 2;
-constexpr uint32_t FA_SMEM_BYTES = 1024 + 6 * FA_TILE_BYTES + 256 + 2048;  // Q, 2 x (K, V), P, barriers, row-maximum exchange
+constexpr uint32_t FA_SMEM_BYTES = 1024 + 7 * FA_TILE_BYTES + 256;  // Q, 2 x (K, V), 2 x P, barriers
 
 struct FaParams {
     int batch, heads, seq;
@@ -61,7 +64,8 @@ __device__ __forceinline__ uint32_t fa_pack_bf16(float lo, float hi)
     return r;
 }
 
-enum { BAR_Q = 0, BAR_K0 = 1, BAR_V0 = 3, BAR_KV_EMPTY0 = 5, BAR_S_FULL0 = 7, BAR_S_FREE0 = 9, BAR_P_FULL = 11, BAR_PV_DONE = 12, BAR_PAIR0 = 13, BAR_COUNT = 17 };
+enum { BAR_Q = 0, BAR_K0 = 1, BAR_V0 = 3, BAR_K_EMPTY0 = 5, BAR_V_EMPTY0 = 7, BAR_S_FULL0 = 9, BAR_S_FREE0 = 11, BAR_P_FULL0 = 13, BAR_PV_DONE0 = 15,
+       BAR_FIN = 17, BAR_COUNT = 18 };
 
 __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(const __grid_constant__ FaMaps maps, const FaParams p)
 {
@@ -72,16 +76,19 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
     const uint32_t q_smem = smem_base;
     auto k_smem = [&](int s) { return smem_base + FA_TILE_BYTES * (1 + 2 * s); };
     auto v_smem = [&](int s) { return smem_base + FA_TILE_BYTES * (2 + 2 * s); };
-    const uint32_t p_smem = smem_base + 5 * FA_TILE_BYTES;
-    const uint32_t bar_base = smem_base + 6 * FA_TILE_BYTES;
+    auto p_smem = [&](int g) { return smem_base + FA_TILE_BYTES * (5 + g); };
+    const uint32_t bar_base = smem_base + 7 * FA_TILE_BYTES;
     auto bar = [&](int i) { return bar_base + 8u * i; };
     const uint32_t tmem_slot = bar_base + 8u * BAR_COUNT;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = (p.seq + FA_BLOCK - 1) / FA_BLOCK;
-    // heavy tiles (late query rows see more keys) are scheduled first
-    const int qt = n_qt - 1 - (int)(blockIdx.x / (p.batch * p.heads));
-    const int bh = blockIdx.x % (p.batch * p.heads);
+    // Consecutive CTAs are the query tiles of ONE (batch, head), heavy tiles (late rows see more keys) first: the CTAs
+    // running at the same time then read the same K/V blocks at about the same time and all but the first reader hit
+    // in L2.  (With the tiles of different heads side by side, each of the 148 resident CTAs streamed its own K/V from
+    // HBM -- 35 GB at seq 8192 -- and the kernel ran at the speed of that traffic, not of the softmax.)
+    const int qt = n_qt - 1 - (int)(blockIdx.x % n_qt);
+    const int bh = blockIdx.x / n_qt;
     const int b = bh / p.heads, h = bh % p.heads;
     const int q0 = qt * FA_BLOCK;
     const int n_blocks = p.causal ? qt + 1 : n_qt;
@@ -92,13 +99,14 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
         for (int s = 0; s < 2; s++) {
             ns_mbar_init(bar(BAR_K0 + s), 1);
             ns_mbar_init(bar(BAR_V0 + s), 1);
-            ns_mbar_init(bar(BAR_KV_EMPTY0 + s), 1);
+            ns_mbar_init(bar(BAR_K_EMPTY0 + s), 1);
+            ns_mbar_init(bar(BAR_V_EMPTY0 + s), 1);
             ns_mbar_init(bar(BAR_S_FULL0 + s), 1);
-            ns_mbar_init(bar(BAR_S_FREE0 + s), 256);
+            ns_mbar_init(bar(BAR_S_FREE0 + s), 128);
+            ns_mbar_init(bar(BAR_P_FULL0 + s), 128);
+            ns_mbar_init(bar(BAR_PV_DONE0 + s), 1);
         }
-        ns_mbar_init(bar(BAR_P_FULL), 256);
-        for (int q = 0; q < 4; q++) ns_mbar_init(bar(BAR_PAIR0 + q), 64);
-        ns_mbar_init(bar(BAR_PV_DONE), 1);
+        ns_mbar_init(bar(BAR_FIN), 256);
         ns_fence_barrier_init();
         ns_fence_proxy_async();
         ns_prefetch_tensormap(&maps.q);
@@ -123,16 +131,28 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
             ns_mbar_expect_tx(bar(BAR_Q), FA_TILE_BYTES);
             ns_tma_load_4d(q_smem, &maps.q, bar(BAR_Q), 0, q0, h, b);
             ns_tma_load_4d(q_smem + FA_HALF_BYTES, &maps.q, bar(BAR_Q), 64, q0, h, b);
-            for (int j = 0; j < n_blocks; j++) {
+            // K_j is wanted early (its scores are computed two blocks ahead of the softmax), V_j late (after the softmax of
+            // block j): K slots are freed by the Q.K^T that read them, V slots by the P.V, and V trails K by one block.
+            auto load_k = [&](int j) {
                 const int s = j & 1;
-                if (j >= 2 && !ns_mbar_wait(bar(BAR_KV_EMPTY0 + s), ((j >> 1) - 1) & 1, abort_flag, p.status, code + 1)) break;
-                const int kv0 = j * FA_BLOCK;
+                if (j >= 2 && !ns_mbar_wait(bar(BAR_K_EMPTY0 + s), ((j >> 1) - 1) & 1, abort_flag, p.status, code + 1)) return false;
                 ns_mbar_expect_tx(bar(BAR_K0 + s), FA_TILE_BYTES);
-                ns_tma_load_4d(k_smem(s), &maps.k, bar(BAR_K0 + s), 0, kv0, h, b);
-                ns_tma_load_4d(k_smem(s) + FA_HALF_BYTES, &maps.k, bar(BAR_K0 + s), 64, kv0, h, b);
+                ns_tma_load_4d(k_smem(s), &maps.k, bar(BAR_K0 + s), 0, j * FA_BLOCK, h, b);
+                ns_tma_load_4d(k_smem(s) + FA_HALF_BYTES, &maps.k, bar(BAR_K0 + s), 64, j * FA_BLOCK, h, b);
+                return true;
+            };
+            auto load_v = [&](int j) {
+                const int s = j & 1;
+                if (j >= 2 && !ns_mbar_wait(bar(BAR_V_EMPTY0 + s), ((j >> 1) - 1) & 1, abort_flag, p.status, code + 1)) return false;
                 ns_mbar_expect_tx(bar(BAR_V0 + s), FA_TILE_BYTES);
-                ns_tma_load_4d(v_smem(s), &maps.v, bar(BAR_V0 + s), 0, kv0, h, b);
-                ns_tma_load_4d(v_smem(s) + FA_HALF_BYTES, &maps.v, bar(BAR_V0 + s), 64, kv0, h, b);
+                ns_tma_load_4d(v_smem(s), &maps.v, bar(BAR_V0 + s), 0, j * FA_BLOCK, h, b);
+                ns_tma_load_4d(v_smem(s) + FA_HALF_BYTES, &maps.v, bar(BAR_V0 + s), 64, j * FA_BLOCK, h, b);
+                return true;
+            };
+            bool pok = true;
+            for (int j = 0; j <= n_blocks && pok; j++) {
+                if (j < n_blocks) pok = load_k(j);
+                if (pok && j >= 1) pok = load_v(j - 1);
             }
         }
     } else if (warp == 1) {
@@ -150,198 +170,231 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
                     const uint32_t off = (kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32;
                     ns_mma_f16(d_tmem, ns_desc_at(desc_k, q_smem + off), ns_desc_at(desc_k, kb + off), idesc_qk, kk > 0 ? 1u : 0u);
                 }
+                ns_tc_commit(bar(BAR_K_EMPTY0 + (j & 1)));
                 ns_tc_commit(bar(BAR_S_FULL0 + (j & 1)));
             };
-            bool ok = ns_mbar_wait(bar(BAR_Q), 0, abort_flag, p.status, code + 2);
-            ok = ok && ns_mbar_wait(bar(BAR_K0), 0, abort_flag, p.status, code + 3);
-            if (ok) {
-                ns_tc_fence_after();
-                issue_qk(0);
-            }
-            for (int j = 0; j < n_blocks && ok; j++) {
-                const int s = j & 1;
-                if (j + 1 < n_blocks) {
-                    const int jn = j + 1;
-                    ok = ns_mbar_wait(bar(BAR_K0 + (jn & 1)), (jn >> 1) & 1, abort_flag, p.status, code + 3);
-                    if (ok && jn >= 2) ok = ns_mbar_wait(bar(BAR_S_FREE0 + (jn & 1)), ((jn >> 1) - 1) & 1, abort_flag, p.status, code + 4);
-                    if (!ok) break;
-                    ns_tc_fence_after();
-                    issue_qk(jn);
-                }
-                ok = ns_mbar_wait(bar(BAR_P_FULL), j & 1, abort_flag, p.status, code + 5);
-                ok = ok && ns_mbar_wait(bar(BAR_V0 + s), (j >> 1) & 1, abort_flag, p.status, code + 6);
-                if (!ok) break;
-                ns_tc_fence_after();
-                const uint32_t o_tmem = tmem_base + 256;
-                const uint32_t vb = v_smem(s);
+            auto issue_pv = [&](int j) {
+                const int g = j & 1;
+                const uint32_t o_tmem = tmem_base + 256 + g * 128;
+                const uint32_t vb = v_smem(g);
+                const uint32_t pb = p_smem(g);
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) {
-                    const uint64_t a_desc = ns_desc_at(desc_k, p_smem + (kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32);
+                    const uint64_t a_desc = ns_desc_at(desc_k, pb + (kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32);
                     const uint64_t b_desc = ns_desc_at(desc_v, vb + kk * (16 * 128));
-                    ns_mma_f16(o_tmem, a_desc, b_desc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    ns_mma_f16(o_tmem, a_desc, b_desc, idesc_pv, (j >= 2 || kk > 0) ? 1u : 0u);
                 }
-                ns_tc_commit(bar(BAR_KV_EMPTY0 + s));
-                ns_tc_commit(bar(BAR_PV_DONE));
+                ns_tc_commit(bar(BAR_V_EMPTY0 + g));
+                ns_tc_commit(bar(BAR_PV_DONE0 + g));
+            };
+            // Whatever is ready is issued: S_j = Q.K_j^T as soon as K_j has landed and the owning group has read S_{j-2} out
+            // of the score buffer (early in its softmax of block j-2), O_g += P_j.V_j as soon as P_j is written.  Scores
+            // are therefore ready two blocks ahead and a group goes from one block to its next without waiting for MMAs.
+            bool ok = ns_mbar_wait(bar(BAR_Q), 0, abort_flag, p.status, code + 2);
+            int qk = 0, pv = 0;
+            long long t_idle = 0;
+            uint32_t spins = 0;
+            while (ok && pv < n_blocks) {
+                bool progressed = false;
+                if (qk < n_blocks && ns_mbar_try_wait(bar(BAR_K0 + (qk & 1)), (qk >> 1) & 1) &&
+                    (qk < 2 || ns_mbar_try_wait(bar(BAR_S_FREE0 + (qk & 1)), ((qk >> 1) - 1) & 1))) {
+                    ns_tc_fence_after();
+                    issue_qk(qk);
+                    qk++;
+                    progressed = true;
+                }
+                if (pv < qk && ns_mbar_try_wait(bar(BAR_P_FULL0 + (pv & 1)), (pv >> 1) & 1) &&
+                    ns_mbar_try_wait(bar(BAR_V0 + (pv & 1)), (pv >> 1) & 1)) {
+                    ns_tc_fence_after();
+                    issue_pv(pv);
+                    pv++;
+                    progressed = true;
+                }
+                if (progressed) {
+                    spins = 0;
+                } else if ((++spins & 0x3F) == 0) {
+                    if (spins == 0x40) t_idle = clock64();
+                    if (*abort_flag != 0) ok = false;
+                    else if (clock64() - t_idle > NS_WAIT_LIMIT_CYCLES) {
+                        *reinterpret_cast<volatile int*>(p.status) = code + 5;
+                        *abort_flag = 1;
+                        __threadfence_block();
+                        ok = false;
+                    }
+                }
             }
         }
     } else {
         // ------------------------------------------------------------ softmax / correction / output
-        // Two warps per accumulator quadrant: warps 2..5 own key columns 0..63 of their 32 rows, warps 6..9 columns
-        // 64..127 (a warp reaches only the tensor-memory lanes of quadrant warp % 4).  With one warp per scheduler
-        // every dependent instruction's latency was exposed; two hide each other's.  The two threads of a row
-        // exchange their partial row maximum through shared memory once per key block.
+        // Two groups of four warps.  Group g owns the key blocks of parity g: its own score buffer S_g, its own P_g in
+        // shared memory, its own output accumulator O_g and its own running maximum and sum, so the two groups never
+        // wait for each other inside the loop and the two warps that share a scheduler are in different phases of their
+        // blocks (one waits on tensor memory or writes P while the other keeps the exponential unit busy).  The two
+        // partial results of a row are merged once, after the last block.
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;        // which 64 key columns / 64 output dims this thread owns
+        const int g = (warp - 2) >> 2;
         const int r = quad * 32 + lane;          // row inside the tile = tensor-memory lane
         const int qi = q0 + r;                   // absolute query position
         const uint32_t lane_addr = tmem_base + (uint32_t(quad * 32) << 16);
-        const uint32_t xch = bar_base + 8u * 24;                     // float [2 buffers][2 halves][128 rows]
-        auto xch_addr = [&](int buf, int hf) { return xch + ((buf * 2 + hf) * 128 + r) * 4; };
-        float m_ref = -INFINITY;                 // reference maximum (raw score units), identical in both threads of a row
-        float l_run = 0.0f;                      // this thread's share of the row sum
-        uint32_t pair_phase = 0;
+        const uint32_t s_addr = lane_addr + g * 128;
+        const uint32_t o_addr = lane_addr + 256 + g * 128;
+        const uint32_t pb = p_smem(g);
+        float m_ref = -INFINITY;                 // reference maximum of this group's blocks (raw score units)
+        float l_run = 0.0f;                      // sum of this group's exponentials relative to m_ref
         bool ok = true;
-        for (int j = 0; j < n_blocks && ok; j++) {
-            ok = ns_mbar_wait(bar(BAR_S_FULL0 + (j & 1)), (j >> 1) & 1, abort_flag, p.status, code + 7);
+        int n_mine = 0;
+        for (int j = g; j < n_blocks && ok; j += 2, n_mine++) {
+            ok = ns_mbar_wait(bar(BAR_S_FULL0 + g), (j >> 1) & 1, abort_flag, p.status, code + 7);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             ns_tc_fence_after();
-            uint32_t sbits[64];
+            uint32_t sb[128];
             {
-                uint32_t t0[32], t1[32];
-                const uint32_t s_addr = lane_addr + (j & 1) * 128 + half * 64;
+                uint32_t t0[32], t1[32], t2[32], t3[32];
                 ns_tmem_ld32(s_addr, t0);
                 ns_tmem_ld32(s_addr + 32, t1);
+                ns_tmem_ld32(s_addr + 64, t2);
+                ns_tmem_ld32(s_addr + 96, t3);
                 ns_tc_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 32; c++) { sbits[c] = t0[c]; sbits[32 + c] = t1[c]; }
+                for (int c = 0; c < 32; c++) { sb[c] = t0[c]; sb[32 + c] = t1[c]; sb[64 + c] = t2[c]; sb[96 + c] = t3[c]; }
             }
             ns_tc_fence_before();
-            ns_mbar_arrive(bar(BAR_S_FREE0 + (j & 1)));
+            ns_mbar_arrive(bar(BAR_S_FREE0 + g));
             // mask: keys after the query (causal) or past the end of the sequence
-            const int kv0 = j * FA_BLOCK + half * 64;
-            const bool need_mask = (p.causal && kv0 + 63 > q0) || kv0 + 64 > p.seq;
-            float mx = -INFINITY;
+            const int kv0 = j * FA_BLOCK;
+            const bool need_mask = (p.causal && kv0 + 127 > q0) || kv0 + 128 > p.seq;
+            float mx;
             if (need_mask) {
+                mx = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 64; c++) {
+                for (int c = 0; c < 128; c++) {
                     const int kj = kv0 + c;
                     const bool dead = (p.causal && kj > qi) || kj >= p.seq;
-                    if (dead) sbits[c] = 0xFF800000u;  // -inf
-                    mx = fmaxf(mx, __uint_as_float(sbits[c]));
+                    if (dead) sb[c] = 0xFF800000u;  // -inf
+                    mx = fmaxf(mx, __uint_as_float(sb[c]));
                 }
             } else {
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int c = 0; c < 64; c += 4) {
-                    m4[0] = fmaxf(m4[0], __uint_as_float(sbits[c])); m4[1] = fmaxf(m4[1], __uint_as_float(sbits[c + 1]));
-                    m4[2] = fmaxf(m4[2], __uint_as_float(sbits[c + 2])); m4[3] = fmaxf(m4[3], __uint_as_float(sbits[c + 3]));
+                for (int c = 0; c < 128; c += 4) {
+                    m4[0] = fmaxf(m4[0], __uint_as_float(sb[c])); m4[1] = fmaxf(m4[1], __uint_as_float(sb[c + 1]));
+                    m4[2] = fmaxf(m4[2], __uint_as_float(sb[c + 2])); m4[3] = fmaxf(m4[3], __uint_as_float(sb[c + 3]));
                 }
                 mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            }
-            // row maximum over both halves
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch_addr(j & 1, half)), "f"(mx) : "memory");
-            ns_mbar_arrive(bar(BAR_PAIR0 + quad));
-            ok = ns_mbar_wait(bar(BAR_PAIR0 + quad), pair_phase, abort_flag, p.status, code + 10);
-            pair_phase ^= 1u;
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            {
-                float other;
-                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(xch_addr(j & 1, half ^ 1)) : "memory");
-                mx = fmaxf(mx, other);
             }
             // reference maximum: raised only when the row maximum outgrew it by more than 8 / scale_log2
             float alpha = 1.0f;
             bool rescale = false;
             if (mx != -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > 8.0f)) {
-                alpha = m_ref == -INFINITY ? 0.0f : exp2f((m_ref - mx) * p.scale_log2);
+                alpha = m_ref == -INFINITY ? 0.0f : fa_exp2((m_ref - mx) * p.scale_log2);
                 rescale = m_ref != -INFINITY;
                 m_ref = mx;
             }
             const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
             const float neg_m = -m_use * p.scale_log2;
             float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t pk[32];
+            uint32_t pk[64];
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) {
+            for (int c = 0; c < 128; c += 4) {
                 // one MUFU each (results below 2^-126 flush to zero, which is what P wants) and one conversion per pair
-                const float p0 = fa_exp2(fmaf(__uint_as_float(sbits[c]), p.scale_log2, neg_m));
-                const float p1 = fa_exp2(fmaf(__uint_as_float(sbits[c + 1]), p.scale_log2, neg_m));
-                const float p2 = fa_exp2(fmaf(__uint_as_float(sbits[c + 2]), p.scale_log2, neg_m));
-                const float p3 = fa_exp2(fmaf(__uint_as_float(sbits[c + 3]), p.scale_log2, neg_m));
+                const float p0 = fa_exp2(fmaf(__uint_as_float(sb[c]), p.scale_log2, neg_m));
+                const float p1 = fa_exp2(fmaf(__uint_as_float(sb[c + 1]), p.scale_log2, neg_m));
+                const float p2 = fa_exp2(fmaf(__uint_as_float(sb[c + 2]), p.scale_log2, neg_m));
+                const float p3 = fa_exp2(fmaf(__uint_as_float(sb[c + 3]), p.scale_log2, neg_m));
                 s4[0] += p0; s4[1] += p1; s4[2] += p2; s4[3] += p3;
                 pk[c >> 1] = fa_pack_bf16(p0, p1);
                 pk[(c >> 1) + 1] = fa_pack_bf16(p2, p3);
             }
             l_run = l_run * alpha + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
-            // P and O belong to the previous P.V until it has completed
-            if (j > 0) {
-                ok = ns_mbar_wait(bar(BAR_PV_DONE), (j - 1) & 1, abort_flag, p.status, code + 8);
+            // P_g and O_g belong to this group's previous P.V until it has completed
+            if (n_mine > 0) {
+                ok = ns_mbar_wait(bar(BAR_PV_DONE0 + g), (n_mine - 1) & 1, abort_flag, p.status, code + 8);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 ns_tc_fence_after();
                 if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-                    for (int c = 0; c < 2; c++) {
+                    for (int c = 0; c < 4; c++) {
                         uint32_t ob[32];
-                        ns_tmem_ld32(lane_addr + 256 + half * 64 + c * 32, ob);
+                        ns_tmem_ld32(o_addr + c * 32, ob);
                         ns_tc_wait_ld();
 #pragma unroll
                         for (int t = 0; t < 32; t++) ob[t] = __float_as_uint(__uint_as_float(ob[t]) * alpha);
-                        ns_tmem_st32(lane_addr + 256 + half * 64 + c * 32, ob);
+                        ns_tmem_st32(o_addr + c * 32, ob);
                     }
                     ns_tc_wait_st();
                 }
             }
             // P_j -> shared memory, K-major halves of 64 keys, 16-byte piece q of row r at q ^ (r & 7)
 #pragma unroll
-            for (int q = 0; q < 8; q++) {
-                const uint32_t addr = p_smem + half * FA_HALF_BYTES + r * 128 + ((q ^ (r & 7)) * 16);
-                ns_st_shared_v4(addr, pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-            }
+            for (int hf = 0; hf < 2; hf++)
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const uint32_t addr = pb + hf * FA_HALF_BYTES + r * 128 + ((q ^ (r & 7)) * 16);
+                    ns_st_shared_v4(addr, pk[hf * 32 + 4 * q], pk[hf * 32 + 4 * q + 1], pk[hf * 32 + 4 * q + 2], pk[hf * 32 + 4 * q + 3]);
+                }
             ns_fence_proxy_async();
             ns_tc_fence_before();
-            ns_mbar_arrive(bar(BAR_P_FULL));
+            ns_mbar_arrive(bar(BAR_P_FULL0 + g));
         }
+        // this group's last P.V (every Q.K^T was issued before it, so Q, K and this group's P buffer are free after it)
+        if (ok && n_mine > 0) {
+            ok = ns_mbar_wait(bar(BAR_PV_DONE0 + g), (n_mine - 1) & 1, abort_flag, p.status, code + 9);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        // merge the two groups: (m, l) of each row go through the first kilobyte of the group's own P buffer
+        const uint32_t xch_mine = pb + r * 8, xch_other = p_smem(g ^ 1) + r * 8;
         if (ok) {
-            ok = ns_mbar_wait(bar(BAR_PV_DONE), (n_blocks - 1) & 1, abort_flag, p.status, code + 9);
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(xch_mine), "f"(m_ref), "f"(l_run) : "memory");
+            ns_tc_fence_before();
+            ns_mbar_arrive(bar(BAR_FIN));
+            ok = ns_mbar_wait(bar(BAR_FIN), 0, abort_flag, p.status, code + 10);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
-            // total row sum = the two threads' shares (both used the same reference maximum throughout)
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch_addr(n_blocks & 1, half)), "f"(l_run) : "memory");
-            ns_mbar_arrive(bar(BAR_PAIR0 + quad));
-            ok = ns_mbar_wait(bar(BAR_PAIR0 + quad), pair_phase, abort_flag, p.status, code + 10);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
-            float other;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(xch_addr(n_blocks & 1, half ^ 1)) : "memory");
             ns_tc_fence_after();
-            const float l_tot = l_run + other;
+            float m_o, l_o;
+            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(m_o), "=f"(l_o) : "r"(xch_other) : "memory");
+            const float m_all = fmaxf(m_ref, m_o);
+            const float a_mine = m_ref == -INFINITY ? 0.0f : fa_exp2((m_ref - m_all) * p.scale_log2);
+            const float a_other = m_o == -INFINITY ? 0.0f : fa_exp2((m_o - m_all) * p.scale_log2);
+            const float l_tot = l_run * a_mine + l_o * a_other;
             const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
-            // O / l -> bf16 -> this warp's 32 rows of its 64-dim half of the P buffer (free now) -> one TMA store
+            const float w_mine = a_mine * inv, w_other = a_other * inv;
+            const uint32_t o_mine = lane_addr + 256 + g * 128, o_other = lane_addr + 256 + (g ^ 1) * 128;
+            // group g finishes output dims [64 g, 64 g + 64): (O_mine w_mine + O_other w_other) -> bf16 -> the upper half of
+            // its P buffer -> one TMA store per warp.  An accumulator that was never written (a group without blocks) holds
+            // anything: its weight is zero and it is not read.
+            const uint32_t stage = pb + FA_HALF_BYTES;
+            const bool have_mine = n_mine > 0, have_other = n_blocks > (g ^ 1);   // uniform over the CTA's groups
 #pragma unroll 1
             for (int c = 0; c < 2; c++) {
-                uint32_t ob[32];
-                ns_tmem_ld32(lane_addr + 256 + half * 64 + c * 32, ob);
+                uint32_t oa[32], ob[32];
+#pragma unroll
+                for (int t = 0; t < 32; t++) { oa[t] = 0u; ob[t] = 0u; }
+                if (have_mine) ns_tmem_ld32(o_mine + g * 64 + c * 32, oa);
+                if (have_other) ns_tmem_ld32(o_other + g * 64 + c * 32, ob);
                 ns_tc_wait_ld();
                 uint32_t w[16];
 #pragma unroll
-                for (int t = 0; t < 16; t++)
-                    w[t] = ns_f32_to_bf16_bits(__uint_as_float(ob[2 * t]) * inv) | (uint32_t(ns_f32_to_bf16_bits(__uint_as_float(ob[2 * t + 1]) * inv)) << 16);
+                for (int t = 0; t < 16; t++) {
+                    // a written accumulator row is finite (a row without live keys in a group's blocks is a sum of zeros)
+                    const float x0 = fmaf(__uint_as_float(ob[2 * t]), w_other, __uint_as_float(oa[2 * t]) * w_mine);
+                    const float x1 = fmaf(__uint_as_float(ob[2 * t + 1]), w_other, __uint_as_float(oa[2 * t + 1]) * w_mine);
+                    w[t] = fa_pack_bf16(x0, x1);
+                }
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const int piece = c * 4 + q;  // 16-byte piece inside the 128-byte row of this half
-                    const uint32_t addr = p_smem + half * FA_HALF_BYTES + r * 128 + ((piece ^ (r & 7)) * 16);
+                    const int piece = c * 4 + q;  // 16-byte piece inside the 128-byte row
+                    const uint32_t addr = stage + r * 128 + ((piece ^ (r & 7)) * 16);
                     ns_st_shared_v4(addr, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
                 }
             }
             ns_fence_proxy_async();
             __syncwarp();
             if (lane == 0 && q0 + quad * 32 < p.seq) {
-                ns_tma_store_4d(&maps.o, p_smem + half * FA_HALF_BYTES + quad * 32 * 128, half * 64, q0 + quad * 32, h, b);
+                ns_tma_store_4d(&maps.o, stage + quad * 32 * 128, g * 64, q0 + quad * 32, h, b);
                 ns_bulk_commit();
                 ns_bulk_wait_read<0>();
             }
