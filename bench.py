@@ -89,6 +89,7 @@ def cpu_reference_tops(rows: int, reps: int):
     """The reference's CPU path for this Linear: float product on the de-quantised operands
     (Backends/Cpu/CpuMatMul.cs via the oracle's restatement), all host threads, `rows` rows of the batch."""
     from oracle import oracle as orc
+    orc.set_threads(len(os.sched_getaffinity(0)))   # all host cores, whatever OMP_NUM_THREADS says
     a = orc.normal((rows, K), 1)
     w_kn = orc.normal((K, NN), 2, 0.02)   # Linear.Weight layout [K, N]
     orc.matmul_f32(a[:64], w_kn, 1, 64, NN, K)
@@ -107,6 +108,7 @@ def run_reference(args, rank):
     rows = 2048
     times = []
     from oracle import oracle as orc
+    orc.set_threads(len(os.sched_getaffinity(0)))   # all host cores: the launcher of multi-rank runs sets OMP_NUM_THREADS=1
     a = orc.normal((rows, K), 1)
     w_kn = orc.normal((K, NN), 2, 0.02)
     for i in range(args.warmup + args.steps):
