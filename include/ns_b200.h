@@ -302,6 +302,26 @@ NS_API int ns_linear_forward(ns_device_t dev, ns_linear_t linear, uint64_t x, ui
 NS_API int ns_linear_forward_host(ns_device_t dev, ns_linear_t linear, const float* x_host, int M, int epilogue, float* y_host, int chunk_rows);
 
 /* ------------------------------------------------------------------------------------------------
+ * Fused row kernels of the decoding step.  With the few rows of a step, time goes to the NUMBER of launches; these
+ * take over a product's epilogue so that the split-K second kernel and the row operator that follows are one launch.
+ * ------------------------------------------------------------------------------------------------ */
+/* The int8 product of `linear` WITHOUT its epilogue: exact int32 partial sums [splits, M, N_local] are left in the device
+ * object's scratch block (valid until the next call on this device that uses the scratch block: another product with a
+ * split K, or decode attention with a split cache); `partial` and `splits` describe them.  M * N_local <= 2^24. */
+NS_API int ns_linear_forward_partial(ns_device_t dev, ns_linear_t linear, uint64_t x, int M, uint64_t* partial, int* splits);
+/* x_out[m,n] = bf16(((float) sum_s partial[s,m,n] * x_scale[m]) * w_scale[n] + bias[n] + residual[m,n]) (residual bf16, may be
+ * 0), then, when gamma != 0: q, q_scale = int8 row quantisation of bf16(LayerNorm(x_out)) -- the input of the next product.
+ * Replaces x + Linear(...) followed by LayerNorm (Layers/Attention.cs:201-205; add_rowvec_f32, add_f32,
+ * layernorm_fused_f32 PtxKernels.Decoding.cs:61-90) for a row-split or K-split product.  q_scale may be x_scale. */
+NS_API int ns_finish_norm_quant(ns_device_t dev, uint64_t partial, int splits, ns_linear_t linear, uint64_t x_scale, uint64_t residual,
+                                int64_t rows, uint64_t x_out, uint64_t gamma, uint64_t beta, float eps, uint64_t q, uint64_t q_scale);
+/* qkv[m, 0:3d] = bf16(dequantised partial sums + bias) of the fused QKV product, and its K and V thirds appended to the cache
+ * at position pos_dev[0] + step (as ns_kv_append).  Replaces the product's epilogue + KeyValueWrite
+ * (Layers/Attention.cs:98-118; kv_write_f32 PtxKernels.Decoding.cs:130-143). */
+NS_API int ns_finish_kv_append(ns_device_t dev, uint64_t partial, int splits, ns_linear_t linear, uint64_t x_scale, int batch, int steps,
+                               uint64_t qkv, ns_kv_cache_t cache, uint64_t page_table, int max_pages, uint64_t pos_dev);
+
+/* ------------------------------------------------------------------------------------------------
  * Tensor parallelism over NCCL.  No counterpart in the reference (single device; Device.cs:54-64).
  * ------------------------------------------------------------------------------------------------ */
 /* y = (partial + bias[col]) + residual: what a row-parallel layer does after its partial sums (float [rows, cols])

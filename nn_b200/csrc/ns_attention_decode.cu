@@ -366,6 +366,21 @@ extern "C" int ns_kv_append(ns_device_t h, ns_kv_cache_t ch, uint64_t k, uint64_
     return NS_OK;
 }
 
+// The pools and geometry of a cache, for kernels in other files that write to it (ns_step_fused.cu).
+struct NsKvCacheView {
+    uint16_t* k_pool;
+    uint16_t* v_pool;
+    int page_size, heads, head_dim;
+};
+int ns_kv_cache_view(ns_kv_cache_t ch, NsKvCacheView* out)
+{
+    NsKvCache* c = reinterpret_cast<NsKvCache*>(ch);
+    NS_REQUIRE(c != nullptr && out != nullptr, NS_ERR_ARGUMENT, "cache is null");
+    out->k_pool = c->k_pool; out->v_pool = c->v_pool;
+    out->page_size = c->page_size; out->heads = c->heads; out->head_dim = c->head_dim;
+    return NS_OK;
+}
+
 // Scratch bytes ns_attention_decode needs for `rows` = batch * heads * steps query rows split `splits` ways.
 static size_t decode_scratch_bytes(int rows, int splits, int dh) { return (size_t)rows * splits * (2 + dh) * sizeof(float); }
 

@@ -32,8 +32,12 @@ struct NsGemmParams {
 // a: [M, K]; b: [N, K] (b_is_kn = false) or [K, N] (b_is_kn = true, bf16 only).
 // partial_override: when non-null, split-K partial sums go there (it must hold
 // k_splits * M * N 32-bit words) instead of the device object's scratch block.
+// deferred_partial / deferred_splits: when non-null (int8 kind only) the epilogue is left to a later kernel: exact
+// int32 partial sums [splits, M, N] stay in the device object's scratch block (one slab when K is not split) and the
+// two out-parameters describe them; no second kernel is launched.
 int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_kn, int M, int N, int K, NsGemmParams p,
-                void* partial_override = nullptr, size_t partial_override_bytes = 0);
+                void* partial_override = nullptr, size_t partial_override_bytes = 0, void** deferred_partial = nullptr,
+                int* deferred_splits = nullptr);
 
 // Tile width / split count the launcher would pick for a shape (also used to size scratch memory).
 void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* tile_n, int* k_splits, bool b_is_kn = false);

@@ -429,8 +429,9 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             // While the tile's MMAs are still running: fetch this row's scale and pull the tile's column scales and
             // biases into L1 (each tile has other columns, so without this every 32-column chunk below would wait
             // for a round trip to L2).
-            cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok && p.k_splits == 1) ? __ldg(&p.a_scale[cx.row]) : 1.0f;
-            if (p.k_splits == 1 && warp == 2) {
+            // (a product that only leaves exact accumulators, p.out == null, has no scales or bias)
+            cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok && p.k_splits == 1 && p.out != nullptr) ? __ldg(&p.a_scale[cx.row]) : 1.0f;
+            if (p.k_splits == 1 && warp == 2 && p.out != nullptr) {
                 const int pc = tn * BN + (lane & 7) * 32;
                 if (lane < BN / 32 && pc < p.N) {
                     if (KIND == NS_KIND_I8) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.w_scale + pc));
@@ -676,8 +677,8 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             cx.row0 = tm * 256 + (int)rank * BM + quad * 32;
             cx.row = cx.row0 + lane;
             cx.row_ok = cx.row < p.M;
-            cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok) ? __ldg(&p.a_scale[cx.row]) : 1.0f;
-            if (warp == 2) {
+            cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok && p.out != nullptr) ? __ldg(&p.a_scale[cx.row]) : 1.0f;
+            if (warp == 2 && p.out != nullptr) {
                 const int pc = tn * BN + (lane & 7) * 32;
                 if (lane < BN / 32 && pc < p.N) {
                     if (KIND == NS_KIND_I8) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.w_scale + pc));
@@ -872,8 +873,10 @@ void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* b
 }
 
 int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_kn, int M, int N, int K, NsGemmParams p,
-                void* partial_override, size_t partial_override_bytes)
+                void* partial_override, size_t partial_override_bytes, void** deferred_partial, int* deferred_splits)
 {
+    const bool deferred = deferred_partial != nullptr && deferred_splits != nullptr;
+    NS_REQUIRE(!deferred || kind == NS_KIND_I8, NS_ERR_ARGUMENT, "a deferred epilogue exists for int8 products only");
     const int elsize = kind == NS_KIND_I8 ? 1 : 2;
     NS_REQUIRE(M > 0 && N > 0 && K > 0, NS_ERR_ARGUMENT, "product with an empty dimension (M=%d N=%d K=%d)", M, N, K);
     NS_REQUIRE(((int64_t)K * elsize) % 16 == 0, NS_ERR_ARGUMENT, "K=%d: a row of %d bytes is not a multiple of 16 bytes", K, K * elsize);
@@ -904,6 +907,14 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
             int rc = ns_scratch_reserve(d, need, &p.partial);
             if (rc != NS_OK) return rc;
         }
+    } else if (deferred) {
+        // K not split: the kernel writes its exact accumulators as the one slab and nothing else
+        void* slab = nullptr;
+        int rc = ns_scratch_reserve(d, (size_t)M * N * 4, &slab);
+        if (rc != NS_OK) return rc;
+        p.raw = reinterpret_cast<int32_t*>(slab);
+        p.out = nullptr;
+        p.epilogue = NS_EPI_NONE;
     }
     CUtensorMap tmA, tmB;
     StoreMaps sm;
@@ -974,6 +985,11 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     else if (!b_is_kn) rc = dispatch_bn<NS_KIND_BF16, false>(d, bn, tmA, tmB, sm, p);
     else rc = dispatch_bn<NS_KIND_BF16, true>(d, bn, tmA, tmB, sm, p);
     if (rc != NS_OK) return rc;
+    if (deferred) {
+        *deferred_partial = p.k_splits > 1 ? p.partial : reinterpret_cast<void*>(p.raw);
+        *deferred_splits = p.k_splits;
+        return NS_OK;
+    }
     if (p.k_splits > 1) {
         int64_t quads = (int64_t)M * ((N + 3) / 4);
         int64_t blocks = (quads + 255) / 256;

@@ -10,6 +10,7 @@
 #include <math.h>
 
 #include "ns_common.cuh"
+#include "ns_rows.cuh"
 
 namespace {
 
@@ -111,6 +112,79 @@ __global__ void __launch_bounds__(ROW_THREADS) ns_layernorm_kernel(const void* _
             for (int j = threadIdx.x; j < cols; j += ROW_THREADS) reinterpret_cast<int8_t*>(y)[base + j] = quant_one(rowbuf[j], sc);
         }
         __syncthreads();
+    }
+}
+
+// ---- register-resident rows (cols % 256 == 0, 16-byte aligned): one CTA per row, see ns_rows.cuh
+template <int VPT, bool F32IN>
+__global__ void ns_quantize_rows_reg_kernel(const void* __restrict__ x, int64_t rows, int cols, int8_t* __restrict__ q, float* __restrict__ scale)
+{
+    ns_pdl_wait();
+    ns_pdl_trigger();
+    __shared__ ns_rows::RowShared sh;
+    int it = 0;
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, it ^= 1) {
+        float v[VPT * 8];
+#pragma unroll
+        for (int j = 0; j < VPT; j++) {
+            const int col = ns_rows::vec_col(j);
+            if (F32IN) {
+                const float* row = reinterpret_cast<const float*>(x) + (size_t)r * cols;
+                const float4 a = *reinterpret_cast<const float4*>(row + col), b = *reinterpret_cast<const float4*>(row + col + 4);
+                v[j * 8] = a.x; v[j * 8 + 1] = a.y; v[j * 8 + 2] = a.z; v[j * 8 + 3] = a.w;
+                v[j * 8 + 4] = b.x; v[j * 8 + 5] = b.y; v[j * 8 + 6] = b.z; v[j * 8 + 7] = b.w;
+            } else {
+                float t[8];
+                ns_rows::widen8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + (size_t)r * cols + col), t);
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[j * 8 + i] = t[i];
+            }
+        }
+        ns_rows::quantize_row<VPT>(v, q + (size_t)r * cols, scale + r, sh.red[it]);   // alternating words: no barrier between rows
+    }
+}
+
+// LayerNorm of bf16 rows -> bf16 rounding -> int8 rows + scales
+template <int VPT>
+__global__ void ns_layernorm_q_reg_kernel(const uint16_t* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                          int64_t rows, int cols, float eps, int8_t* __restrict__ y, float* __restrict__ y_scale)
+{
+    ns_pdl_wait();
+    ns_pdl_trigger();
+    __shared__ ns_rows::RowShared sh;
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        float v[VPT * 8];
+#pragma unroll
+        for (int j = 0; j < VPT; j++) {
+            float t[8];
+            ns_rows::widen8(*reinterpret_cast<const uint4*>(x + (size_t)r * cols + ns_rows::vec_col(j)), t);
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[j * 8 + i] = t[i];
+        }
+        ns_rows::layernorm_quantize_row<VPT>(v, gamma, beta, eps, cols, y + (size_t)r * cols, y_scale + r, sh);
+    }
+}
+
+inline unsigned grid_rows(const NsDevice* d, int64_t rows);
+
+template <bool F32IN>
+cudaError_t launch_quantize_reg(NsDevice* d, unsigned threads, int vpt, const void* x, int64_t rows, int cols, int8_t* q, float* scale)
+{
+    const dim3 grid(grid_rows(d, rows)), block(threads);
+    switch (vpt) {
+        case 1: return ns_launch_plain(ns_quantize_rows_reg_kernel<1, F32IN>, grid, block, 0, d->stream, x, rows, cols, q, scale);
+        case 2: return ns_launch_plain(ns_quantize_rows_reg_kernel<2, F32IN>, grid, block, 0, d->stream, x, rows, cols, q, scale);
+        default: return ns_launch_plain(ns_quantize_rows_reg_kernel<4, F32IN>, grid, block, 0, d->stream, x, rows, cols, q, scale);
+    }
+}
+cudaError_t launch_layernorm_q_reg(NsDevice* d, unsigned threads, int vpt, const uint16_t* x, const float* gamma, const float* beta, int64_t rows,
+                                   int cols, float eps, int8_t* y, float* y_scale)
+{
+    const dim3 grid(grid_rows(d, rows)), block(threads);
+    switch (vpt) {
+        case 1: return ns_launch_plain(ns_layernorm_q_reg_kernel<1>, grid, block, 0, d->stream, x, gamma, beta, rows, cols, eps, y, y_scale);
+        case 2: return ns_launch_plain(ns_layernorm_q_reg_kernel<2>, grid, block, 0, d->stream, x, gamma, beta, rows, cols, eps, y, y_scale);
+        default: return ns_launch_plain(ns_layernorm_q_reg_kernel<4>, grid, block, 0, d->stream, x, gamma, beta, rows, cols, eps, y, y_scale);
     }
 }
 
@@ -252,6 +326,15 @@ extern "C" int ns_quantize_rows_i8(ns_device_t h, uint64_t x, int in_dtype, int6
     NS_REQUIRE(in_dtype == NS_F32 || in_dtype == NS_BF16, NS_ERR_ARGUMENT, "ns_quantize_rows_i8: input must be NS_F32 or NS_BF16");
     NS_REQUIRE(rows >= 0 && cols > 0, NS_ERR_ARGUMENT, "ns_quantize_rows_i8: bad shape");
     if (rows == 0) return NS_OK;
+    unsigned threads = 0;
+    int vpt = 0;
+    if (((x | q) & 15) == 0 && ns_rows::row_shape(cols, &threads, &vpt)) {
+        if (in_dtype == NS_F32)
+            NS_CUDA(launch_quantize_reg<true>(d, threads, vpt, reinterpret_cast<const void*>(x), rows, cols, reinterpret_cast<int8_t*>(q), reinterpret_cast<float*>(scale)));
+        else
+            NS_CUDA(launch_quantize_reg<false>(d, threads, vpt, reinterpret_cast<const void*>(x), rows, cols, reinterpret_cast<int8_t*>(q), reinterpret_cast<float*>(scale)));
+        return NS_OK;
+    }
     ns_launch_plain(ns_quantize_rows_kernel, dim3(grid_rows(d, rows)), dim3(ROW_THREADS), 0, d->stream, reinterpret_cast<const void*>(x), in_dtype, rows, cols,
                                                                               reinterpret_cast<int8_t*>(q), reinterpret_cast<float*>(scale));
     NS_CUDA(cudaGetLastError());
@@ -268,6 +351,14 @@ extern "C" int ns_layernorm(ns_device_t h, uint64_t x, int in_dtype, uint64_t ga
     NS_REQUIRE(out_dtype != NS_I8 || y_scale != 0, NS_ERR_ARGUMENT, "ns_layernorm: int8 output needs a scale buffer");
     NS_REQUIRE(rows >= 0 && cols > 0 && cols <= 16384, NS_ERR_ARGUMENT, "ns_layernorm: cols must be in [1, 16384]");
     if (rows == 0) return NS_OK;
+    unsigned threads = 0;
+    int vpt = 0;
+    if (in_dtype == NS_BF16 && out_dtype == NS_I8 && ((x | y | gamma | beta) & 15) == 0 && ns_rows::row_shape(cols, &threads, &vpt)) {
+        // the decoder's case: the row lives in the registers of its CTA
+        NS_CUDA(launch_layernorm_q_reg(d, threads, vpt, reinterpret_cast<const uint16_t*>(x), reinterpret_cast<const float*>(gamma),
+                                       reinterpret_cast<const float*>(beta), rows, cols, eps, reinterpret_cast<int8_t*>(y), reinterpret_cast<float*>(y_scale)));
+        return NS_OK;
+    }
     size_t smem = (size_t)cols * sizeof(float);
     static bool configured[64] = {false};
     if (smem > 48 * 1024 && !configured[d->ordinal]) {

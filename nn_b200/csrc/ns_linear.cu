@@ -175,3 +175,28 @@ int ns_linear_forward_on(NsDevice* d, NsLinear* L, const void* x, const float* x
     p.bias = epilogue == NS_EPI_NONE ? nullptr : L->bias;
     return ns_gemm_run(d, L->mode == NS_I8 ? NS_KIND_I8 : NS_KIND_BF16, x, L->w, false, M, L->N_loc, L->K_loc, p);
 }
+
+// The int8 product of a layer without its epilogue: exact int32 partial sums [splits, M, N_local] stay in the device
+// object's scratch block for the row kernel that follows (ns_finish_norm_quant, ns_finish_kv_append).
+extern "C" int ns_linear_forward_partial(ns_device_t h, ns_linear_t lh, uint64_t x, int M, uint64_t* partial, int* splits)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NsLinear* L = reinterpret_cast<NsLinear*>(lh);
+    NS_REQUIRE(L && x && partial && splits, NS_ERR_ARGUMENT, "ns_linear_forward_partial: null argument");
+    NS_REQUIRE(L->mode == NS_I8, NS_ERR_ARGUMENT, "ns_linear_forward_partial: int8 layers only");
+    NS_REQUIRE(M > 0 && (int64_t)M * L->N_loc <= (int64_t)1 << 24, NS_ERR_ARGUMENT,
+               "ns_linear_forward_partial: meant for the few rows of a decoding step (M * N <= 2^24), got M=%d N=%d", M, L->N_loc);
+    NsGemmParams p = {};
+    p.epilogue = NS_EPI_NONE;
+    p.out_dtype = NS_F32;
+    p.residual_dtype = NS_F32;
+    void* ptr = nullptr;
+    int s = 0;
+    rc = ns_gemm_run(d, NS_KIND_I8, reinterpret_cast<const void*>(x), L->w, false, M, L->N_loc, L->K_loc, p, nullptr, 0, &ptr, &s);
+    if (rc != NS_OK) return rc;
+    *partial = reinterpret_cast<uint64_t>(ptr);
+    *splits = s;
+    return NS_OK;
+}

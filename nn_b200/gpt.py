@@ -65,10 +65,20 @@ class _Linear:
         N.call("ns_linear_forward", self.dev.handle, self.handle, C.c_uint64(x), C.c_uint64(x_scale), m, epilogue, C.c_uint64(residual),
                residual_dtype, out_dtype, C.c_uint64(y))
 
+    def forward_partial(self, x: int, m: int):
+        """The product without its epilogue: (address, splits) of the int32 partial sums in the device's scratch block."""
+        ptr, splits = C.c_uint64(), C.c_int()
+        N.call("ns_linear_forward_partial", self.dev.handle, self.handle, C.c_uint64(x), m, C.byref(ptr), C.byref(splits))
+        return ptr.value, splits.value
+
     def close(self):
         if self.handle:
             N.call("ns_linear_destroy", self.handle)
             self.handle = None
+
+
+# Up to this many rows a pass uses the fused row kernels (ns_finish_*): one launch less per product whose K is split.
+FUSED_MAX_ROWS = 256
 
 
 class GptW8A8:
@@ -128,6 +138,7 @@ class GptW8A8:
             self.am_val, self.am_idx = dev.empty(batch), dev.empty(batch, N.NS_I32)
             self.am_vals, self.am_idxs = dev.empty(batch * tp_size), dev.empty(batch * tp_size, N.NS_I32)
         self.length = 0          # host mirror of the device position (DecodingContext.Length, Layers/Decoding.cs:75)
+        self.fused = True        # few-row passes use the fused row kernels; False keeps one kernel per operator
         self.graph = None
         self.launches_per_step = 0
 
@@ -154,6 +165,8 @@ class GptW8A8:
         assert m <= self.max_rows and self.length + steps <= cfg.context, "DecodingContext.BeginStep: capacity exceeded"
         self._n = 0
         eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
+        if self.tp == 1 and m <= FUSED_MAX_ROWS and self.fused:
+            return self._forward_fused(steps)
         x_in, x_out = self.x
         N.call("ns_embed_pos", h, self.ids.ptr, self.tok.ptr, self.pos_table.ptr, N.NS_BF16, self.pos.ptr, B, steps, D, cfg.vocab, cfg.context,
                N.NS_BF16, x_in.ptr)
@@ -202,6 +215,60 @@ class GptW8A8:
             self._n += 6
         N.call("ns_add_i32", h, self.pos.ptr, steps)
         self._n += 1
+        self.x = [x_in, x_out]
+
+    def _forward_fused(self, steps: int) -> None:
+        """The same pass for few rows (a decoding step) with the products' epilogues moved into the row kernels that
+        follow them: per layer QKV product, dequantise + bias + KV append, attention, quantise, out product, dequantise +
+        bias + residual + LayerNorm + quantise, FF1 (bias + GELU epilogue), quantise, FF2 product, dequantise + bias +
+        residual + the NEXT LayerNorm + quantise: 10 launches (FF1 may add a split-K reduction of its own)."""
+        cfg, dev, B = self.cfg, self.dev, self.batch
+        h, D, dh, dl = dev.handle, cfg.dim, cfg.head_dim, self.d_loc
+        m = B * steps
+        eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
+        x_in, x_out = self.x
+        N.call("ns_embed_pos", h, self.ids.ptr, self.tok.ptr, self.pos_table.ptr, N.NS_BF16, self.pos.ptr, B, steps, D, cfg.vocab, cfg.context,
+               N.NS_BF16, x_in.ptr)
+        first = self.layers[0]
+        N.call("ns_layernorm", h, x_in.ptr, N.NS_BF16, first["ln1"][0].ptr, first["ln1"][1].ptr, C.c_int64(m), D, eps, N.NS_I8, self.hq.ptr, self.hq_scale.ptr)
+        self._n += 2
+        head_from_last_rows = steps == 1        # the final LayerNorm can ride on the last layer's FF2 only if every row is a last row
+        for i, (L, cache) in enumerate(zip(self.layers, self.caches)):
+            part, sp = L["qkv"].forward_partial(self.hq.ptr, m)
+            N.call("ns_finish_kv_append", h, C.c_uint64(part), sp, L["qkv"].handle, self.hq_scale.ptr, B, steps, self.qkv.ptr, cache,
+                   self.page_table.ptr, self.max_pages, self.pos.ptr)
+            q = self.qkv.ptr
+            N.call("ns_attention_decode", h, cache, C.c_uint64(q), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
+                   self.max_pages, self.pos.ptr, B, steps, scale)
+            N.call("ns_quantize_rows_i8", h, self.attn.ptr, N.NS_BF16, C.c_int64(m), dl, self.hq.ptr, self.hq_scale.ptr)
+            part, sp = L["out"].forward_partial(self.hq.ptr, m)
+            N.call("ns_finish_norm_quant", h, C.c_uint64(part), sp, L["out"].handle, self.hq_scale.ptr, x_in.ptr, C.c_int64(m), x_out.ptr,
+                   L["ln2"][0].ptr, L["ln2"][1].ptr, eps, self.hq.ptr, self.hq_scale.ptr)
+            x_in, x_out = x_out, x_in
+            # (FF1 keeps its own bias + GELU epilogue: moving the GELU of 8192 columns into a 64-CTA row kernel was slower)
+            L["ff1"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS_GELU, N.NS_BF16, self.ffh.ptr)
+            N.call("ns_quantize_rows_i8", h, self.ffh.ptr, N.NS_BF16, C.c_int64(m), self.ff_loc, self.hq.ptr, self.hq_scale.ptr)
+            part, sp = L["ff2"].forward_partial(self.hq.ptr, m)
+            if i + 1 < len(self.layers):
+                g, bta = self.layers[i + 1]["ln1"]
+            elif head_from_last_rows:
+                g, bta = self.lnf
+            else:
+                g = bta = None
+            N.call("ns_finish_norm_quant", h, C.c_uint64(part), sp, L["ff2"].handle, self.hq_scale.ptr, x_in.ptr, C.c_int64(m), x_out.ptr,
+                   g.ptr if g else 0, bta.ptr if bta else 0, eps, self.hq.ptr, self.hq_scale.ptr)
+            x_in, x_out = x_out, x_in
+            self._n += 10
+        if not head_from_last_rows:
+            N.call("ns_d2d_2d_async", h, C.c_uint64(self.last.ptr), C.c_uint64(D * 2), C.c_uint64(x_in.ptr + (steps - 1) * D * 2),
+                   C.c_uint64(steps * D * 2), C.c_uint64(D * 2), C.c_uint64(B))
+            N.call("ns_layernorm", h, C.c_uint64(self.last.ptr), N.NS_BF16, self.lnf[0].ptr, self.lnf[1].ptr, C.c_int64(B), D, eps, N.NS_I8,
+                   self.hq.ptr, self.hq_scale.ptr)
+            self._n += 2
+        self.head.forward(self.hq.ptr, self.hq_scale.ptr, B, N.EPI_BIAS, N.NS_F32, self.logits.ptr)
+        N.call("ns_argmax_i32", h, self.logits.ptr, B, cfg.vocab, C.c_int64(cfg.vocab), self.ids.ptr)
+        N.call("ns_add_i32", h, self.pos.ptr, steps)
+        self._n += 3
         self.x = [x_in, x_out]
 
     # ------------------------------------------------------------------ generator (CharGpt.Generate, CharGpt.cs:231-318)
