@@ -1,6 +1,6 @@
 """Benchmark of the hot path: int8 QuantizedMatMul (int8 x int8 -> int32, per-channel dequant + bias epilogue).
 
-Workload (BASELINE config "int8 QuantizedMatMul sweep", the largest M): A [8192, 4096] float ~N(0,1) quantised per
+Workload (benchmark configuration "int8 QuantizedMatMul sweep", the largest M): A [8192, 4096] float ~N(0,1) quantised per
 row, W [4096, 4096] ~N(0,0.02) quantised per output channel, bias ~N(0,0.01), float output.  One step = one pass
 of the product over one batch of 8192 rows.  With N > 1 GPUs every rank runs its own batch of rows against its own
 copy of the weights (batch sharding, no data-path collective): weak scaling.
@@ -279,6 +279,9 @@ def run_case(spec: str):
       qmatmul_i8:M            int8 product, K = N = 4096, bias epilogue, f32 out
       attention_decode:L      batch 64, 32 heads, head_dim 128, cache length L
       attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
+      gpt_decode:LAYERS       the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64)
+                              cut to LAYERS layers: prompt of 512, then three decoding steps (seeded numpy weights);
+                              prints the device time of a replayed step
     """
     import numpy as np
     from nn_b200 import native as N
@@ -321,6 +324,32 @@ def run_case(spec: str):
         st = (C.c_int64 * 3)(H * S * 128, S * 128, 128)
         for _ in range(3):
             N.call("ns_attention_prefill", dev.handle, q.ptr, k.ptr, v.ptr, o.ptr, B, H, S, 128, st, st, st, st, C.c_float(0.0884), 1)
+    elif name == "gpt_decode":
+        from nn_b200.gpt import GptConfig, GptW8A8
+        layers, B, prompt_len = int(arg or 2), 64, 512
+        cfg = GptConfig(vocab=32000, dim=2048, heads=16, layers=layers, ff_dim=8192, context=768)
+        rng = np.random.default_rng(4)
+        D, FF, V = cfg.dim, cfg.ff_dim, cfg.vocab
+        nrm = lambda *shape, s=0.02: (rng.standard_normal(shape, dtype=np.float32) * s)
+        w = {"tok": nrm(V, D), "pos": nrm(cfg.context, D), "lnf_g": 1.0 + nrm(D, s=0.05), "lnf_b": nrm(D), "head_w": nrm(D, V), "head_b": nrm(V, s=0.01),
+             "l0.ln1_g": 1.0 + nrm(D, s=0.05), "l0.ln1_b": nrm(D), "l0.ln2_g": 1.0 + nrm(D, s=0.05), "l0.ln2_b": nrm(D),
+             "l0.qkv_w": nrm(D, 3 * D), "l0.qkv_b": nrm(3 * D, s=0.01), "l0.out_w": nrm(D, D), "l0.out_b": nrm(D, s=0.01),
+             "l0.ff1_w": nrm(D, FF), "l0.ff1_b": nrm(FF, s=0.01), "l0.ff2_w": nrm(FF, D), "l0.ff2_b": nrm(D, s=0.01)}
+        model = GptW8A8(dev, cfg, w, B, max_prefill=prompt_len, share_layer_weights=True)   # every layer its own device copy
+        model.prefill(rng.integers(0, V, (B, prompt_len)).astype(np.int32))
+        for _ in range(3):
+            model.step(False)
+        dev.synchronize()
+        e0, e1 = dev.event(), dev.event()
+        model.step(True)
+        model.step(True)
+        dev.record(e0)
+        for _ in range(20):
+            model.step(True)
+        dev.record(e1)
+        ms = dev.elapsed_ms(e0, e1) / 20
+        print(json.dumps({"case": spec, "ok": True, "ms_per_replayed_step": ms, "tokens_per_s": B / ms * 1e3, "layers": layers}))
+        return
     else:
         raise SystemExit(f"unknown case {spec}")
     dev.synchronize()

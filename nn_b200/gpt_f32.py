@@ -9,7 +9,7 @@ last position.  Ids, the position and the sampled token are float-encoded values
 reference (Layers/Decoding.cs:69,81-82), so one recorded graph serves every position.
 
 It exists to show the operator surface is a drop-in (same results as the CPU backend on the same weights) and to run
-BASELINE config 1; the fast path for large models is ``nn_b200.gpt.GptW8A8``.
+benchmark configuration 1; the fast path for large models is ``nn_b200.gpt.GptW8A8``.
 """
 from __future__ import annotations
 

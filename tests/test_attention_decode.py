@@ -3,7 +3,7 @@
 bf16 keys/values/queries, float math; tolerance 1e-2 relative on bf16 outputs (|e-a| <= tol*max(1,|e|)).
 Covers the reference's CachedDecodingMatchesFull / BatchedDecoding pattern (DecodingTests.cs:69-142): a prefill
 followed by single steps equals full causal attention; identity and shuffled page tables give the same answer;
-BASELINE config 4's decode case (batch 64, 32 heads, cache length 4096, head_dim 128) on sampled (batch, head) pairs.
+benchmark configuration 4's decode case (batch 64, 32 heads, cache length 4096, head_dim 128) on sampled (batch, head) pairs.
 """
 import ctypes as C
 

@@ -1,7 +1,7 @@
 """Causal attention over a whole sequence (ns_attention_prefill, tcgen05) against the oracle's reference-order
 attention: scale, additive mask, row maximum, exp, float sum, normalise, . V (Layers/Attention.cs:54-90,
 CpuBackend.Decoding.cs:9-41) on the same bf16-rounded inputs.  Tolerance 1e-2 relative on bf16 outputs.
-BASELINE config 4: [batch 8, heads 32, seq, 128], seq in {512, 2048, 8192}, scale 1/sqrt(128), seed 3.
+benchmark configuration 4: [batch 8, heads 32, seq, 128], seq in {512, 2048, 8192}, scale 1/sqrt(128), seed 3.
 """
 import ctypes as C
 

@@ -1,6 +1,6 @@
 """bf16 x bf16 -> float product (ns_matmul_bf16) against the oracle: <= 1e-2 relative, |e-a| <= tol*max(1,|e|).
 
-Config: squares {1024, 4096, 8192} and the skinny shape M=8, K=4096, N=14336 (BASELINE config "bf16 dense MatMul",
+Config: squares {1024, 4096, 8192} and the skinny shape M=8, K=4096, N=14336 (benchmark configuration "bf16 dense MatMul",
 seed 2); B is stored [K, N] as in the config (and as Linear.Weight in the reference) and also [N, K].
 """
 import numpy as np

@@ -2,7 +2,7 @@
 
 Accumulators must be bit-exact; the float epilogue is computed in the same operation order as the oracle, so
 it is compared bit-exactly too (tolerance 0) except through GELU, where tanhf differs by ulps (1e-5).
-Config: K = N = 4096, M in {1, 16, 128, 2048, 8192} (BASELINE config "int8 QuantizedMatMul sweep", seed 1).
+Config: K = N = 4096, M in {1, 16, 128, 2048, 8192} (benchmark configuration "int8 QuantizedMatMul sweep", seed 1).
 """
 import ctypes as C
 

@@ -2,7 +2,7 @@
 float32 decoder (the reference's CPU backend restated), restating the reference's decoding tests:
 CachedDecodingMatchesFull (DecodingTests.cs:69-98: TinyGpt vocab 11, dim 16, 4 heads, ffDim 32, 2 layers, ctx 12,
 prefill 4 then 6 single steps == full forward, 1e-4), BatchedDecoding (:100-142, B=3 == each sequence alone),
-GraphReplay (:144-189, graph == direct over 8 steps), and BASELINE config 1 (char-level GPT: vocab 96, d_model 128,
+GraphReplay (:144-189, graph == direct over 8 steps), and benchmark configuration 1 (char-level GPT: vocab 96, d_model 128,
 4 layers, 4 heads, FFN 512, context 128, prompt 32, greedy 128 tokens: logits <= 1e-4, token ids equal, one context
 reset at the 97th token).
 """

@@ -1,5 +1,5 @@
 """The int8 / bf16 decoder (nn_b200.gpt.GptW8A8) against the CPU oracle decoder (oracle/model.py) on a reduced clone
-of BASELINE config 5 (same head_dim 128 and operator sequence, fewer/narrower layers so the CPU finishes in seconds).
+of benchmark configuration 5 (same head_dim 128 and operator sequence, fewer/narrower layers so the CPU finishes in seconds).
 
 Protocol (greedy argmax can flip on near-ties under reordered arithmetic): teacher-forced per-step comparison of the
 logits and of the argmax wherever the oracle's top-2 gap exceeds the tolerance.  Every operator is held to its own
