@@ -224,9 +224,34 @@ __global__ void __launch_bounds__(ROW_THREADS) ns_argmax_i32_kernel(const float*
         const float* xs = x + (size_t)r * row_stride;
         float best = -INFINITY;
         int idx = 0x7fffffff;
-        for (int j = threadIdx.x; j < cols; j += ROW_THREADS) {
-            float v = xs[j];
-            if (idx == 0x7fffffff || v > best) { best = v; idx = j; }
+        if ((cols & 3) == 0 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0) {
+            // 16-byte loads, four in flight; a thread meets its indices in increasing order, so "strictly greater" keeps the
+            // first maximum
+            const float4* x4 = reinterpret_cast<const float4*>(xs);
+            const int n4 = cols >> 2;
+            for (int j0 = threadIdx.x; j0 < n4; j0 += 4 * ROW_THREADS) {
+                float4 t[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = j0 + u * ROW_THREADS;
+                    t[u] = j < n4 ? x4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = (j0 + u * ROW_THREADS) * 4;
+                    if (j < cols) {
+                        const float v[4] = {t[u].x, t[u].y, t[u].z, t[u].w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            if (idx == 0x7fffffff || v[e] > best) { best = v[e]; idx = j + e; }
+                    }
+                }
+            }
+        } else {
+            for (int j = threadIdx.x; j < cols; j += ROW_THREADS) {
+                float v = xs[j];
+                if (idx == 0x7fffffff || v > best) { best = v; idx = j; }
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
