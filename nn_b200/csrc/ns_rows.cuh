@@ -113,6 +113,73 @@ __device__ __forceinline__ void layernorm_quantize_row(float (&x)[VPT * 8], cons
     quantize_row<VPT>(x, q_row, scale_out, sh.red[2]);
 }
 
+// ---- many rows: one WARP per row.  With thousands of rows every SM holds dozens of independent warps, each with all of
+// its row's loads in flight at once, which a CTA walking its rows one after another (a chain of three barriers per
+// row) cannot match: LayerNorm -> int8 of 32768 x 2048 ran at 1.1 TB/s with a CTA per row.  Lane l holds the vectors
+// k * 32 + l (k < VEC), cols = VEC * 256.
+__device__ __forceinline__ float warp_reduce(float v, bool is_max)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float t = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, t) : v + t;
+    }
+    return v;
+}
+
+template <int VEC>
+__device__ __forceinline__ void warp_quantize_row(const float (&x)[VEC * 8], int8_t* __restrict__ q_row, float* __restrict__ scale_out, int lane)
+{
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC * 8; i++) amax = fmaxf(amax, fabsf(x[i]));
+    amax = warp_reduce(amax, true);
+    const float sc = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    if (lane == 0) *scale_out = sc;
+#pragma unroll
+    for (int k = 0; k < VEC; k++) {
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            lo |= (uint32_t)(uint8_t)quant_one(x[k * 8 + t], sc) << (8 * t);
+            hi |= (uint32_t)(uint8_t)quant_one(x[k * 8 + 4 + t], sc) << (8 * t);
+        }
+        *reinterpret_cast<uint2*>(q_row + (size_t)(k * 32 + lane) * 8) = make_uint2(lo, hi);
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void warp_layernorm_quantize_row(float (&x)[VEC * 8], const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                            float eps, int8_t* __restrict__ q_row, float* __restrict__ scale_out, int lane)
+{
+    constexpr int COLS = VEC * 256;
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC * 8; i++) s += x[i];
+    const float mean = warp_reduce(s, false) / (float)COLS;
+    float v2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC * 8; i++) { const float d = x[i] - mean; v2 += d * d; }
+    const float inv = 1.0f / sqrtf(warp_reduce(v2, false) / (float)COLS + eps);
+#pragma unroll
+    for (int k = 0; k < VEC; k++) {
+        const int col = (k * 32 + lane) * 8;
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + col)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + col + 4));
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + col)), b1 = __ldg(reinterpret_cast<const float4*>(beta + col + 4));
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            const float h = __fadd_rn(__fmul_rn(__fmul_rn(x[k * 8 + t] - mean, inv), g[t]), b[t]);
+            x[k * 8 + t] = ns_bf16_bits_to_f32(ns_f32_to_bf16_bits(h));
+        }
+    }
+    warp_quantize_row<VEC>(x, q_row, scale_out, lane);
+}
+
+// Rows at and above this count take the warp-per-row kernels.
+constexpr int64_t MANY_ROWS = 2048;
+
 // CTA shape for rows of `cols` elements (cols % 256 == 0): threads = min(256, cols / 8), vectors per thread = cols / 8 /
 // threads.  Returns false when the row does not fit the register-resident kernels (more than 4 vectors per thread).
 inline bool row_shape(int cols, unsigned* threads, int* vpt)

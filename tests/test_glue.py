@@ -10,7 +10,7 @@ from nn_b200 import native as N
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 16), (5, 100), (64, 2048), (33, 8192)])
+@pytest.mark.parametrize("rows,cols", [(1, 16), (5, 100), (64, 2048), (33, 8192), (130, 512), (2500, 2048), (2100, 4096), (2049, 1024)])
 def test_quantize_rows_bit_exact(dev, orc, rows, cols):
     x = orc.normal((rows, cols), 81, 1.5)
     x[0, :] = 0.0  # all-zero row -> scale 1
@@ -26,7 +26,7 @@ def test_quantize_rows_bit_exact(dev, orc, rows, cols):
         assert np.array_equal(q, dq.download((rows, cols)))
 
 
-@pytest.mark.parametrize("rows,cols", [(3, 128), (64, 2048), (7, 8192)])
+@pytest.mark.parametrize("rows,cols", [(3, 128), (64, 2048), (7, 8192), (40, 512), (2500, 2048), (2049, 1024), (2050, 4096)])
 def test_layernorm_variants(dev, orc, rows, cols):
     x = orc.normal((rows, cols), 91, 2.0)
     g, b = orc.normal((cols,), 92, 0.5, 1.0), orc.normal((cols,), 93, 0.1)
