@@ -486,7 +486,8 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// CTA-pair kernel for large products (weights stored [N, K], no K split).
+// CTA-pair kernel for large products (no K split; weights stored [N, K] or, for bf16, [K, N] read through MN-major
+// descriptors as in the single-CTA kernel).
 //
 // With one CTA per 128 x 256 tile every k-block needs 48 KB from L2 (16 KB of A, 32 KB of B) for 512 tensor-core
 // cycles of int8 (or bf16) work, and an SM takes in about 64 bytes per cycle: 768 cycles of loading per 512 cycles
@@ -528,7 +529,7 @@ __device__ __forceinline__ void pair_coords(const NsGemmParams& p, int item, int
 
 constexpr int PAIR_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
 
-template <int KIND>
+template <int KIND, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ StoreMaps sm, const NsGemmParams p)
@@ -606,7 +607,13 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const uint32_t bar = ns_mapa(full_bar(s), 0);
                     const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
                     ns_tma_load_2d_pair(a_dst, &tmA, bar, kb * ELEMS_PER_KB, row0);
-                    ns_tma_load_2d_pair(a_dst + Cfg::A_BYTES, &tmB, bar, kb * ELEMS_PER_KB, brow0);
+                    if (!B_MN) {
+                        ns_tma_load_2d_pair(a_dst + Cfg::A_BYTES, &tmB, bar, kb * ELEMS_PER_KB, brow0);
+                    } else {
+                        // B stored [K, N]: this CTA's 128 columns as two boxes of 64 columns x 64 rows of K
+                        ns_tma_load_2d_pair(a_dst + Cfg::A_BYTES, &tmB, bar, brow0, kb * 64);
+                        ns_tma_load_2d_pair(a_dst + Cfg::A_BYTES + 64 * 128, &tmB, bar, brow0 + 64, kb * 64);
+                    }
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
             }
@@ -619,8 +626,9 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer (even CTA only)
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = KIND == NS_KIND_I8 ? ns_idesc(2, 1, 0, 0, 256, BN) : ns_idesc(1, 1, 0, 0, 256, BN);
+            constexpr uint32_t idesc = KIND == NS_KIND_I8 ? ns_idesc(2, 1, 0, 0, 256, BN) : ns_idesc(1, 1, 0, B_MN ? 1 : 0, 256, BN);
             const uint64_t desc_k = ns_desc_base(16, 1024);
+            const uint64_t desc_mn = ns_desc_base(64 * 128, 1024);     // MN-major: 64-column blocks 8 KB apart, 8 k-rows 1 KB apart
             int s = 0;
             uint32_t phase = 0;
             int local = 0;
@@ -641,7 +649,7 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                     for (int kk = 0; kk < 4; kk++) {
                         const uint64_t a_desc = ns_desc_at(desc_k, a_addr + kk * 32);
-                        const uint64_t b_desc = ns_desc_at(desc_k, b_addr + kk * 32);
+                        const uint64_t b_desc = B_MN ? ns_desc_at(desc_mn, b_addr + kk * (16 * 128)) : ns_desc_at(desc_k, b_addr + kk * 32);
                         const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
                         if (KIND == NS_KIND_I8) ns_mma_i8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
                         else ns_mma_f16_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
@@ -797,10 +805,10 @@ int launch_gemm(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, con
     return NS_OK;
 }
 
-template <int KIND>
+template <int KIND, bool B_MN>
 int launch_pair(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p)
 {
-    auto kernel = ns_gemm_pair_kernel<KIND>;
+    auto kernel = ns_gemm_pair_kernel<KIND, B_MN>;
     static int max_clusters[64] = {0};
     if (max_clusters[d->ordinal] == 0) {
         NS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg::SMEM_BYTES));
@@ -889,7 +897,7 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     // Large products with [N, K] weights go to the CTA-pair kernel (256 x 256 tiles over two SMs): whenever 256-wide
     // tiles without a K split were chosen and there are at least two row tiles.  Tuning override 512 forces it, 256
     // forces the single-CTA kernel.
-    const bool pair = !b_is_kn && splits == 1 && M > BM && (d->force_bn == 512 || (d->force_bn == 0 && bn == 256));
+    const bool pair = splits == 1 && M > BM && (d->force_bn == 512 || (d->force_bn == 0 && bn == 256));
     p.kb_per_split = (p.k_blocks + splits - 1) / splits;
     p.k_splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
     p.tiles_m = pair ? (M + 255) / 256 : (M + BM - 1) / BM;
@@ -980,7 +988,11 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
             }
         }
     }
-    if (pair) rc = kind == NS_KIND_I8 ? launch_pair<NS_KIND_I8>(d, tmA, tmB, sm, p) : launch_pair<NS_KIND_BF16>(d, tmA, tmB, sm, p);
+    if (pair) {
+        if (kind == NS_KIND_I8) rc = launch_pair<NS_KIND_I8, false>(d, tmA, tmB, sm, p);
+        else if (!b_is_kn) rc = launch_pair<NS_KIND_BF16, false>(d, tmA, tmB, sm, p);
+        else rc = launch_pair<NS_KIND_BF16, true>(d, tmA, tmB, sm, p);
+    }
     else if (kind == NS_KIND_I8) rc = dispatch_bn<NS_KIND_I8, false>(d, bn, tmA, tmB, sm, p);
     else if (!b_is_kn) rc = dispatch_bn<NS_KIND_BF16, false>(d, bn, tmA, tmB, sm, p);
     else rc = dispatch_bn<NS_KIND_BF16, true>(d, bn, tmA, tmB, sm, p);

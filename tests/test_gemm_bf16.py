@@ -67,15 +67,16 @@ def test_baseline_shapes(dev, orc, m, n, k):
         assert np.all(np.abs(exp_cols - got_cols) <= bound)
 
 
+@pytest.mark.parametrize("transB", [False, True])
 @pytest.mark.parametrize("m,n,k", [(256, 256, 64), (257, 520, 1032), (900, 264, 512)])
-def test_cta_pair_kernel(dev, orc, m, n, k):
-    """The two-CTA kernel forced onto small shapes (B stored [N, K]; the [K, N] layout stays on the single-CTA kernel)."""
+def test_cta_pair_kernel(dev, orc, m, n, k, transB):
+    """The two-CTA kernel forced onto small shapes, B stored [N, K] and [K, N]."""
     a = orc.round_bf16(orc.normal((m, k), 31))
-    b = orc.round_bf16(orc.normal((n, k), 32))
+    b = orc.round_bf16(orc.normal((n, k) if transB else (k, n), 32))
     dev.tune(512, 1)
     try:
-        c = _run(dev, a, b, m, n, k, True, out_dtype=N.NS_F32)[0]
+        c = _run(dev, a, b, m, n, k, transB, out_dtype=N.NS_F32)[0]
     finally:
         dev.tune(0, 0)
-    exp = orc.matmul_bf16(a, b, b_is_nk=True)
+    exp = orc.matmul_bf16(a, b, b_is_nk=transB)
     assert orc.close(exp, c, 1e-4), f"max err {orc.max_err(exp, c)}"
