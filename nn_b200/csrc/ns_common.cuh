@@ -412,5 +412,12 @@ NS_DEVINL uint16_t ns_f32_to_bf16_bits(float f)
 {
     return __bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
+// two floats -> two bf16 (round to nearest even) in one word, `lo` in the low half: one conversion instruction
+NS_DEVINL uint32_t ns_pack_bf16x2(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 
 #endif  // __CUDACC__

@@ -39,5 +39,29 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
                 void* partial_override = nullptr, size_t partial_override_bytes = 0, void** deferred_partial = nullptr,
                 int* deferred_splits = nullptr);
 
+// The row-streaming int8 kernel for 1..8 activation rows (ns_gemv_i8.cu).  `p` must hold M, N, K, the epilogue
+// fields, out / raw and the scale, bias and residual pointers.
+bool ns_gemv_i8_fits(int M, int K);
+int ns_gemv_i8_run(NsDevice* d, const NsGemmParams& p, const void* a, const void* w);
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float ns_gemm_residual(const NsGemmParams& p, size_t idx)
+{
+    if (p.residual_dtype == NS_BF16) return ns_bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.residual)[idx]);
+    return reinterpret_cast<const float*>(p.residual)[idx];
+}
+
+// exact int32 sum -> output value (without the residual): ((float)acc * a_scale) * w_scale (+ bias (, GELU))
+__device__ __forceinline__ float ns_gemm_finish_i8(const NsGemmParams& p, int32_t acc, float a_scale, float w_scale, float bias)
+{
+    float v = __int2float_rn(acc);
+    v = __fmul_rn(v, a_scale);
+    v = __fmul_rn(v, w_scale);
+    if (p.epilogue != NS_EPI_NONE) v = __fadd_rn(v, bias);
+    if (p.epilogue == NS_EPI_BIAS_GELU) v = ns_gelu_tanh(v);
+    return v;
+}
+#endif
+
 // Tile width / split count the launcher would pick for a shape (also used to size scratch memory).
 void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* tile_n, int* k_splits, bool b_is_kn = false);

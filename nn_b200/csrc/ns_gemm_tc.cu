@@ -70,14 +70,8 @@ __device__ __forceinline__ void tile_coords(const NsGemmParams& p, int item, int
 template <int KIND>
 __device__ __forceinline__ float finish_value(const NsGemmParams& p, uint32_t bits, float a_scale, float w_scale, float bias)
 {
-    float v;
-    if (KIND == NS_KIND_I8) {
-        v = __int2float_rn(static_cast<int32_t>(bits));
-        v = __fmul_rn(v, a_scale);
-        v = __fmul_rn(v, w_scale);
-    } else {
-        v = __uint_as_float(bits);
-    }
+    if (KIND == NS_KIND_I8) return ns_gemm_finish_i8(p, static_cast<int32_t>(bits), a_scale, w_scale, bias);
+    float v = __uint_as_float(bits);
     if (p.epilogue != NS_EPI_NONE) v = __fadd_rn(v, bias);
     if (p.epilogue == NS_EPI_BIAS_GELU) v = ns_gelu_tanh(v);
     return v;
@@ -85,8 +79,7 @@ __device__ __forceinline__ float finish_value(const NsGemmParams& p, uint32_t bi
 
 __device__ __forceinline__ float load_residual(const NsGemmParams& p, size_t idx)
 {
-    if (p.residual_dtype == NS_BF16) return ns_bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.residual)[idx]);
-    return reinterpret_cast<const float*>(p.residual)[idx];
+    return ns_gemm_residual(p, idx);
 }
 
 // Adds residual[row, col0 .. col0+32) to v.  Vector loads when the row pitch allows.
@@ -190,12 +183,21 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
 
     float v[32];
     const bool vec_ok = p.vec_cols && col0 + 32 <= p.N;
+    float4 bv[8];
+    if (vec_ok && p.epilogue != NS_EPI_NONE) {
+        const float4* b4 = reinterpret_cast<const float4*>(p.bias + col0);
+#pragma unroll
+        for (int q = 0; q < 8; q++) bv[q] = __ldg(b4 + q);
+    }
     if (KIND == NS_KIND_I8) {
         if (vec_ok) {
             const float4* ws4 = reinterpret_cast<const float4*>(p.w_scale + col0);
+            float4 wsv[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) wsv[q] = __ldg(ws4 + q);
 #pragma unroll
             for (int q = 0; q < 8; q++) {
-                const float4 w4 = __ldg(ws4 + q);
+                const float4 w4 = wsv[q];
                 v[4 * q] = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)r[4 * q]), cx.a_scale), w4.x);
                 v[4 * q + 1] = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)r[4 * q + 1]), cx.a_scale), w4.y);
                 v[4 * q + 2] = __fmul_rn(__fmul_rn(__int2float_rn((int32_t)r[4 * q + 2]), cx.a_scale), w4.z);
@@ -212,10 +214,9 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
     }
     if (p.epilogue != NS_EPI_NONE) {
         if (vec_ok) {
-            const float4* b4 = reinterpret_cast<const float4*>(p.bias + col0);
 #pragma unroll
             for (int q = 0; q < 8; q++) {
-                const float4 t = __ldg(b4 + q);
+                const float4 t = bv[q];
                 v[4 * q] = __fadd_rn(v[4 * q], t.x); v[4 * q + 1] = __fadd_rn(v[4 * q + 1], t.y);
                 v[4 * q + 2] = __fadd_rn(v[4 * q + 2], t.z); v[4 * q + 3] = __fadd_rn(v[4 * q + 3], t.w);
             }
@@ -248,7 +249,7 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
             uint32_t w[32];
 #pragma unroll
             for (int j = 0; j < 16; j++)
-                w[j] = ns_f32_to_bf16_bits(v[2 * j]) | (uint32_t(ns_f32_to_bf16_bits(v[2 * j + 1])) << 16);
+                w[j] = ns_pack_bf16x2(v[2 * j], v[2 * j + 1]);
             stage_and_store<16>(cx.bufs + (cx.single ? 0 : (cx.nbuf & 1)) * EPI_BUF_BYTES, cx.lane, w, &sm.out, col0, cx.row0, 0, false, cx.single);
             cx.nbuf++;
         } else if (cx.row_ok) {
@@ -699,19 +700,14 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ns_tc_fence_after();
             const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
             const bool warp_has_rows = cx.row0 < p.M;
-            uint32_t ra[32], rb[32];
+            uint32_t ra[32];
             __syncwarp();
-            ns_tmem_ld32(t_row + c_begin * 32, ra);
 #pragma unroll 1
-            for (int c = c_begin; c < c_end; c += 2) {
+            for (int c = c_begin; c < c_end; c++) {
+                ns_tmem_ld32(t_row + c * 32, ra);
                 ns_tc_wait_ld();
                 __syncwarp();
-                ns_tmem_ld32(t_row + (c + 1) * 32, rb);
                 if (warp_has_rows && tn * BN + c * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, ra, tn * BN + c * 32);
-                ns_tc_wait_ld();
-                __syncwarp();
-                if (c + 2 < c_end) ns_tmem_ld32(t_row + (c + 2) * 32, ra);
-                if (warp_has_rows && tn * BN + (c + 1) * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, rb, tn * BN + (c + 1) * 32);
             }
             ns_tc_fence_before();
             __syncwarp();
@@ -891,6 +887,11 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     NS_REQUIRE(!(b_is_kn && kind == NS_KIND_I8), NS_ERR_ARGUMENT, "int8 weights must be stored [N,K]");
     NS_REQUIRE(!b_is_kn || (N % 8) == 0, NS_ERR_ARGUMENT, "N=%d must be a multiple of 8 when B is stored [K,N]", N);
     p.M = M; p.N = N; p.K = K;
+    // One to eight rows of int8 activations: the row-streaming kernel on the CUDA cores (a tuning override keeps
+    // the tensor-core kernels, as does a deferred epilogue).
+    if (kind == NS_KIND_I8 && !deferred && d->force_bn == 0 && d->force_splits == 0 && ns_gemv_i8_fits(M, K) &&
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0)
+        return ns_gemv_i8_run(d, p, a, b);
     p.k_blocks = (int)(((int64_t)K * elsize + BKB - 1) / BKB);
     int bn, splits;
     ns_gemm_choose_tiling(d, M, N, p.k_blocks, &bn, &splits, b_is_kn);

@@ -150,3 +150,41 @@ def test_cta_pair_kernel_bit_exact(dev, orc, M, Nn, K, epi):
     exp = orc.dequant_epilogue(acc, a_s, w_s, bias, residual=res)
     assert np.array_equal(y.view(np.uint32), exp.view(np.uint32)), f"max err {orc.max_err(exp, y)}"
     assert np.array_equal(yb, orc.round_bf16(exp))
+
+
+@pytest.mark.parametrize("M,Nn,K", [(1, 4096, 4096), (1, 37, 16), (2, 130, 528), (3, 1000, 1040), (4, 512, 16384), (5, 96, 2048),
+                                    (8, 2048, 8192), (9, 333, 4096), (16, 1024, 8192), (16, 6, 512), (8, 6, 512), (7, 10, 16), (13, 4096, 2048), (2, 256, 32768),
+                                    (1, 64, 32768), (1, 72, 16384), (4, 64, 32768), (8, 40, 16384), (2, 64, 16400)])
+def test_row_streaming_kernel_bit_exact(dev, orc, M, Nn, K):
+    """One to eight rows take the row-streaming kernel on the CUDA cores (every register shape: 1/2/4/8 rows x 1/2/4
+    pieces per warp; ragged K pieces, ragged column groups, fewer columns than CTAs, one piece for a CTA whose
+    epilogue needs two warps); nine to sixteen rows stay on the tensor cores.  Accumulators and every epilogue must
+    equal the oracle's, and the tensor-core kernels' (forced by a tuning override) bit for bit."""
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=21)
+    res = orc.normal((M, Nn), 78)
+    acc = orc.qmatmul_i8_acc(aq, wq)
+    y, raw = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS)
+    assert np.array_equal(raw, acc), f"accumulators differ at {np.argwhere(raw != acc)[:4]}"
+    exp = orc.dequant_epilogue(acc, a_s, w_s, bias)
+    assert np.array_equal(y.view(np.uint32), exp.view(np.uint32))
+    y, _ = _run(dev, aq, a_s, wq, w_s, None, epilogue=N.EPI_NONE, want_raw=False)
+    assert np.array_equal(y.view(np.uint32), orc.dequant_epilogue(acc, a_s, w_s).view(np.uint32))
+    y, _ = _run(dev, aq, a_s, wq, w_s, bias, residual=res, epilogue=N.EPI_BIAS_RESIDUAL, want_raw=False)
+    exp_r = orc.dequant_epilogue(acc, a_s, w_s, bias, residual=res)
+    assert np.array_equal(y.view(np.uint32), exp_r.view(np.uint32))
+    res_b = orc.round_bf16(res)
+    yb, _ = _run(dev, aq, a_s, wq, w_s, bias, residual=res_b, epilogue=N.EPI_BIAS_RESIDUAL, out_dtype=N.NS_BF16, residual_dtype=N.NS_BF16,
+                 want_raw=False)
+    assert np.array_equal(yb, orc.round_bf16(orc.dequant_epilogue(acc, a_s, w_s, bias, residual=orc.widen_bf16(res_b))))
+    yg, _ = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS_GELU, want_raw=False)
+    assert orc.close(orc.dequant_epilogue(acc, a_s, w_s, bias, act=1), yg, 1e-5)
+    # the tensor-core path on the same operands
+    dev.tune(64, 2 if K >= 512 else 1)
+    try:
+        y_tc, raw_tc = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS)
+        yg_tc, _ = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS_GELU, want_raw=False)
+    finally:
+        dev.tune(0, 0)
+    assert np.array_equal(raw_tc, acc)
+    assert np.array_equal(y_tc.view(np.uint32), exp.view(np.uint32))
+    assert np.array_equal(yg_tc.view(np.uint32), yg.view(np.uint32)), "GELU epilogue differs between the two kernels"
