@@ -11,12 +11,12 @@
 // Warp w of a CTA owns pieces w * CPW .. w * CPW + CPW - 1 of EVERY row the CTA handles, so the activations that meet
 // those bytes (MR rows x CPW x 16 bytes per lane) are loaded once into registers and stay there.  A CTA takes a
 // contiguous range of N / gridDim.x columns (the ranges differ by at most one column, so all SMs finish together)
-// and walks it four columns at a time; the loads of the next four columns are issued as soon as a register slot is
-// consumed, so every warp keeps four pieces (2 KB) in flight.  Per column: 4 * MR dp4a per lane and piece, then a
-// transposing butterfly over the lanes (MR - 1 + log2(32 / MR) shuffles instead of 5 * MR) that leaves row r's sum
-// in lane r * 32 / MR, one shared-memory word per (warp, column, row), and after a CTA barrier 4 * MR threads add the
-// warps' words and apply the epilogue.  Their per-column operands were fetched before the barrier, and the words are
-// double-buffered, so a group costs one barrier.
+// and walks it four (eight for one or two rows) columns at a time; the loads of the next group are issued as soon as
+// a register slot is consumed, so every warp keeps four or eight pieces (2 - 4 KB) in flight.  Per column: 4 * MR
+// dp4a per lane and piece, then a transposing butterfly over the lanes (MR - 1 + log2(32 / MR) shuffles instead of
+// 5 * MR) that leaves row r's sum in lane r * 32 / MR, one shared-memory word per (warp, column, row), and after a
+// CTA barrier one thread per (column, row) adds the warps' words and applies the epilogue.  Its per-column operands
+// were fetched before the barrier, and the words are double-buffered, so a group costs one barrier.
 //
 // Measured (K = N = 4096, CUDA events, operands rotated beyond L2): 5.5 / 6.3 / 7.9 us at 1 / 4 / 8 rows against
 // 9.9 - 10.0 us for the tensor-core kernel with split K and its second pass.  At 16 rows the dp4a and shuffle issue
@@ -25,7 +25,9 @@
 
 namespace {
 
-constexpr int GV_COLS = 4;         // columns per group (= pieces in flight per warp and activation piece)
+// columns per group (= pieces in flight per warp and activation piece): eight for one or two rows, where the
+// registers allow it and a CTA's whole share of columns is then fetched in one or two rounds of loads
+__host__ __device__ constexpr int gv_cols(int mr) { return mr <= 2 ? 8 : 4; }
 constexpr int GV_MAX_WARPS = 16;
 
 __device__ __forceinline__ int4 gv_load_stream(const int8_t* ptr)
@@ -62,6 +64,7 @@ template <int MR, int CPW>
 __global__ void __launch_bounds__(GV_MAX_WARPS * 32, 1)
 ns_gemv_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const int8_t* __restrict__ w)
 {
+    constexpr int GV_COLS = gv_cols(MR);
     __shared__ int red[2][GV_MAX_WARPS][GV_COLS][MR];
     ns_pdl_wait();
     ns_pdl_trigger();
@@ -93,7 +96,7 @@ ns_gemv_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const int8
         for (int m = 0; m < MR; m++)
             x[c][m] = (m < p.M && kv[c]) ? __ldg(reinterpret_cast<const int4*>(a + (size_t)m * p.K + kb[c])) : make_int4(0, 0, 0, 0);
 
-    // the threads of the epilogue: thread t finishes (row t / 4, column t % 4) of every group
+    // the threads of the epilogue: thread t finishes (row t / GV_COLS, column t % GV_COLS) of every group
     const int f_row = threadIdx.x / GV_COLS, f_col = threadIdx.x % GV_COLS;
     const bool f_row_ok = threadIdx.x < GV_COLS * MR && f_row < p.M;
     const float a_scale = (f_row_ok && p.out != nullptr) ? __ldg(&p.a_scale[f_row]) : 1.0f;
@@ -150,6 +153,7 @@ ns_gemv_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const int8
 template <int MR, int CPW>
 int launch_gemv(NsDevice* d, const NsGemmParams& p, const void* a, const void* w, int warps)
 {
+    constexpr int GV_COLS = gv_cols(MR);
     auto kernel = ns_gemv_i8_kernel<MR, CPW>;
     static int ctas_per_sm[GV_MAX_WARPS + 1] = {0};
     if (ctas_per_sm[warps] == 0) {
@@ -185,9 +189,10 @@ int ns_gemv_i8_run(NsDevice* d, const NsGemmParams& p, const void* a, const void
     const int pieces = (p.K + 511) / 512;
     int cpw = 1;
     while (pieces > GV_MAX_WARPS * cpw) cpw *= 2;
-    // one warp per CPW pieces of a row; the epilogue needs 4 * MR threads (a warp without a piece adds zeros)
+    // one warp per CPW pieces of a row; the epilogue needs a thread per (column of a group, row) (a warp without a
+    // piece adds zeros)
     int warps = (pieces + cpw - 1) / cpw;
-    if (warps * 32 < GV_COLS * mr) warps = (GV_COLS * mr + 31) / 32;
+    if (warps * 32 < gv_cols(mr) * mr) warps = (gv_cols(mr) * mr + 31) / 32;
 #define GV_CASE(MR_, CPW_) \
     if (mr == MR_ && cpw == CPW_) return launch_gemv<MR_, CPW_>(d, p, a, w, warps);
     GV_CASE(1, 1) GV_CASE(1, 2) GV_CASE(1, 4)
