@@ -277,6 +277,7 @@ def run_case(spec: str):
     """Small fixed cases for profiler captures (`ncu ... python bench.py --case NAME:ARGS`): three launches of one
     kernel on device-generated inputs, nothing timed.
       qmatmul_i8:M            int8 product, K = N = 4096, bias epilogue, f32 out
+      qmatmul_i8_rows:M       int8 product of M <= 8 rows with 32768 x 8192 weights (268 MB, beyond L2): the row-streaming kernel
       attention_decode:L      batch 64, 32 heads, head_dim 128, cache length L
       attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
       gpt_decode:LAYERS       the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64)
@@ -299,6 +300,17 @@ def run_case(spec: str):
         y = dev.empty(m * NN)
         for _ in range(3):
             N.call("ns_qmatmul_i8", dev.handle, a.ptr, a_s.ptr, w.ptr, w_s.ptr, b.ptr, 0, 0, m, NN, K, N.EPI_BIAS, N.NS_F32, y.ptr, 0)
+    elif name == "qmatmul_i8_rows":
+        m, n_, k_ = int(arg or 1), 32768, 8192
+        a, w = dev.empty(m * k_, N.NS_I8), dev.empty(n_ * k_, N.NS_I8)
+        N.call("ns_fill_normal", dev.handle, a.ptr, N.NS_I8, C.c_int64(m * k_), 1, 0.0, 40.0)
+        N.call("ns_fill_normal", dev.handle, w.ptr, N.NS_I8, C.c_int64(n_ * k_), 9, 0.0, 40.0)
+        a_s, w_s, b = dev.empty(m), dev.empty(n_), dev.empty(n_)
+        for t, cnt in ((a_s, m), (w_s, n_), (b, n_)):
+            N.call("ns_fill_normal", dev.handle, t.ptr, N.NS_F32, C.c_int64(cnt), 5, 1.0, 0.1)
+        y = dev.empty(m * n_)
+        for _ in range(3):
+            N.call("ns_qmatmul_i8", dev.handle, a.ptr, a_s.ptr, w.ptr, w_s.ptr, b.ptr, 0, 0, m, n_, k_, N.EPI_BIAS, N.NS_F32, y.ptr, 0)
     elif name == "attention_decode":
         B, heads, dh, L, ps = 64, 32, 128, int(arg or 1024), 64
         max_pages = (L + ps) // ps
