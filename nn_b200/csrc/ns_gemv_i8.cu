@@ -18,7 +18,7 @@
 // CTA barrier one thread per (column, row) adds the warps' words and applies the epilogue.  Its per-column operands
 // were fetched before the barrier, and the words are double-buffered, so a group costs one barrier.
 //
-// Measured (K = N = 4096, CUDA events, operands rotated beyond L2): 5.5 / 6.3 / 7.9 us at 1 / 4 / 8 rows against
+// Measured (K = N = 4096, CUDA events, operands rotated beyond L2): 5.3 / 5.5 / 8.0 us at 1 / 4 / 8 rows against
 // 9.9 - 10.0 us for the tensor-core kernel with split K and its second pass.  At 16 rows the dp4a and shuffle issue
 // rate makes this kernel slower (11.5 against 10.2 us), so products of nine rows and more stay on the tensor cores.
 #include "ns_gemm.cuh"
@@ -189,6 +189,10 @@ int ns_gemv_i8_run(NsDevice* d, const NsGemmParams& p, const void* a, const void
     const int pieces = (p.K + 511) / 512;
     int cpw = 1;
     while (pieces > GV_MAX_WARPS * cpw) cpw *= 2;
+    // three and four rows: two pieces per warp halve the lane-summing butterflies per dp4a, which is what bounds them
+    // (32768 x 8192 weights: 57.7 -> 43.6 us = 6.17 TB/s); at eight rows the same change gained 6 % there and lost
+    // at K = 2048, so eight rows keep one piece per warp
+    if (mr == 4 && cpw == 1 && pieces >= 4) cpw = 2;
     // one warp per CPW pieces of a row; the epilogue needs a thread per (column of a group, row) (a warp without a
     // piece adds zeros)
     int warps = (pieces + cpw - 1) / cpw;
