@@ -55,6 +55,7 @@ typedef struct ns_graph_s* ns_graph_t;
 typedef struct ns_linear_s* ns_linear_t;
 typedef struct ns_kv_cache_s* ns_kv_cache_t;
 typedef struct ns_comm_s* ns_comm_t;
+typedef struct ns_peer_group_s* ns_peer_group_t;
 
 /* ------------------------------------------------------------------------------------------------
  * Runtime.  Replaces CudaBackend's constructor and CudaDriver's cuInit, cuDeviceGet, cuCtx.. and cuStream..
@@ -344,6 +345,25 @@ NS_API int ns_allgather(ns_device_t dev, ns_comm_t comm, uint64_t src, uint64_t 
 NS_API int ns_comm_async_error(ns_comm_t comm, int* nccl_result);
 NS_API int ns_comm_abort(ns_comm_t comm);     /* after a peer failed: does not wait for the peers */
 NS_API int ns_comm_destroy(ns_comm_t comm);
+
+/* The exchange step of the tensor-parallel decoder over peer memory (one process per GPU, up to 8 ranks of one machine).
+ * Every rank creates a group (one device block: flags + two slots of `slot_bytes`), hands its 64-byte handle to the other
+ * ranks by the host program's own means, and connects with the `world` handles in rank order.  New: the reference has no
+ * multi-GPU code (Tensor.To goes through a host array, Tensor.cs:244-253). */
+NS_API int ns_peer_group_create(ns_device_t dev, int rank, int world, uint64_t slot_bytes, ns_peer_group_t* group);
+NS_API int ns_peer_group_handle(ns_peer_group_t group, void* handle64);
+NS_API int ns_peer_group_connect(ns_peer_group_t group, const void* handles);
+/* Device address of this rank's slot (0 or 1): the row-parallel product writes its float partial rows [rows, cols] there. */
+NS_API int ns_peer_group_slot(ns_peer_group_t group, int slot, uint64_t* ptr);
+/* x_out[m,n] = bf16(sum over ranks, in rank order, of their slot's partial[m,n] + bias[n] + residual[m,n]) (bias float, residual
+ * bf16, either may be 0), then, when gamma != 0: q, q_scale = int8 row quantisation of bf16(LayerNorm(x_out)).  One kernel in
+ * place of all-reduce + add_rowvec_f32 + add_f32 + layernorm_fused_f32 (Layers/Attention.cs:201-205,
+ * PtxKernels.Decoding.cs:61-90).  Every rank must call it for the same slot in the same order; a rank that waits for a peer
+ * for about a second gives up and reports NS_ERR_KERNEL at the next ns_stream_sync.  rows <= 64 x SM count, cols a multiple
+ * of 256 up to 8192. */
+NS_API int ns_tp_reduce_norm_quant(ns_device_t dev, ns_peer_group_t group, int slot, uint64_t bias, uint64_t residual, int64_t rows, int cols,
+                                   uint64_t x_out, uint64_t gamma, uint64_t beta, float eps, uint64_t q, uint64_t q_scale);
+NS_API int ns_peer_group_destroy(ns_peer_group_t group);
 
 #ifdef __cplusplus
 }

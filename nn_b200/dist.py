@@ -51,6 +51,27 @@ def init_comm(dev: Device):
     return comm, rank, world
 
 
+def make_peer_group(dev: Device, rank: int, world: int, slot_bytes: int):
+    """A peer-memory group for ns_tp_reduce_norm_quant: every rank's 64-byte IPC handle is gathered over gloo."""
+    import torch
+    import torch.distributed as dist
+
+    group = C.c_void_p()
+    N.call("ns_peer_group_create", dev.handle, rank, world, C.c_uint64(slot_bytes), C.byref(group))
+    mine = C.create_string_buffer(64)
+    N.call("ns_peer_group_handle", group, mine)
+    if world > 1:
+        if not dist.is_initialized():
+            dist.init_process_group("gloo")
+        parts = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(parts, torch.frombuffer(bytearray(mine.raw), dtype=torch.uint8).clone())
+        handles = b"".join(bytes(t.numpy().tobytes()) for t in parts)
+    else:
+        handles = mine.raw
+    N.call("ns_peer_group_connect", group, handles)
+    return group
+
+
 def barrier() -> None:
     import torch.distributed as dist
 

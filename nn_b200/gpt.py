@@ -90,7 +90,7 @@ class GptW8A8:
     """
 
     def __init__(self, dev: Device, cfg: GptConfig, weights: dict, batch: int, max_prefill: int, tp_rank: int = 0, tp_size: int = 1,
-                 comm=None, page_size: int = 64, share_layer_weights: bool = False):
+                 comm=None, page_size: int = 64, share_layer_weights: bool = False, peer_exchange: bool = True):
         assert cfg.dim % cfg.heads == 0 and cfg.heads % tp_size == 0 and cfg.ff_dim % tp_size == 0 and cfg.vocab % tp_size == 0
         assert tp_size == 1 or comm is not None
         self.dev, self.cfg, self.batch, self.rank, self.tp, self.comm = dev, cfg, batch, tp_rank, tp_size, comm
@@ -130,6 +130,17 @@ class GptW8A8:
         self.attn = dev.empty(R * self.d_loc, N.NS_BF16)
         self.ffh = dev.empty(R * self.ff_loc, N.NS_BF16)
         self.partial = dev.empty(R * D, N.NS_F32) if tp_size > 1 else None
+        # few-row passes on several GPUs exchange their partial rows through peer memory (one fused kernel per half-layer)
+        self.peer = None
+        self.peer_slots = None
+        if tp_size > 1 and peer_exchange and D % 256 == 0 and D <= 8192:
+            from . import dist
+            self.peer = dist.make_peer_group(dev, tp_rank, tp_size, FUSED_MAX_ROWS * D * 4)
+            self.peer_slots = []
+            for slot in range(2):
+                ptr = C.c_uint64()
+                N.call("ns_peer_group_slot", self.peer, slot, C.byref(ptr))
+                self.peer_slots.append(ptr.value)
         self.last = dev.empty(batch * D, N.NS_BF16)
         self.logits = dev.empty(batch * self.v_loc, N.NS_F32)
         self.ids = dev.zeros(self.max_rows, N.NS_I32)          # prompt ids during prefill; ids[0:batch] = current tokens while decoding
@@ -167,6 +178,8 @@ class GptW8A8:
         eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
         if self.tp == 1 and m <= FUSED_MAX_ROWS and self.fused:
             return self._forward_fused(steps)
+        if self.tp > 1 and m <= FUSED_MAX_ROWS and self.fused and self.peer is not None:
+            return self._forward_tp_fused(steps)
         x_in, x_out = self.x
         N.call("ns_embed_pos", h, self.ids.ptr, self.tok.ptr, self.pos_table.ptr, N.NS_BF16, self.pos.ptr, B, steps, D, cfg.vocab, cfg.context,
                N.NS_BF16, x_in.ptr)
@@ -271,6 +284,61 @@ class GptW8A8:
         self._n += 3
         self.x = [x_in, x_out]
 
+    def _forward_tp_fused(self, steps: int) -> None:
+        """The few-row pass on several GPUs: as _forward_fused, but a row-parallel product (attention output, FF2) writes
+        its float partial rows into this rank's peer-memory slot and ONE kernel sums the ranks' rows, adds bias and
+        residual, and normalises + quantises for the next product (ns_tp_reduce_norm_quant) -- no NCCL call inside a
+        layer.  The vocabulary-split head keeps its (value, index) gather over NCCL."""
+        cfg, dev, B = self.cfg, self.dev, self.batch
+        h, D, dh, dl = dev.handle, cfg.dim, cfg.head_dim, self.d_loc
+        m = B * steps
+        eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
+        x_in, x_out = self.x
+        N.call("ns_embed_pos", h, self.ids.ptr, self.tok.ptr, self.pos_table.ptr, N.NS_BF16, self.pos.ptr, B, steps, D, cfg.vocab, cfg.context,
+               N.NS_BF16, x_in.ptr)
+        first = self.layers[0]
+        N.call("ns_layernorm", h, x_in.ptr, N.NS_BF16, first["ln1"][0].ptr, first["ln1"][1].ptr, C.c_int64(m), D, eps, N.NS_I8, self.hq.ptr, self.hq_scale.ptr)
+        self._n += 2
+        head_from_last_rows = steps == 1
+        for i, (L, cache) in enumerate(zip(self.layers, self.caches)):
+            part, sp = L["qkv"].forward_partial(self.hq.ptr, m)
+            N.call("ns_finish_kv_append", h, C.c_uint64(part), sp, L["qkv"].handle, self.hq_scale.ptr, B, steps, self.qkv.ptr, cache,
+                   self.page_table.ptr, self.max_pages, self.pos.ptr)
+            N.call("ns_attention_decode", h, cache, C.c_uint64(self.qkv.ptr), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
+                   self.max_pages, self.pos.ptr, B, steps, scale)
+            N.call("ns_quantize_rows_i8", h, self.attn.ptr, N.NS_BF16, C.c_int64(m), dl, self.hq.ptr, self.hq_scale.ptr)
+            L["out"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_NONE, N.NS_F32, self.peer_slots[0])
+            N.call("ns_tp_reduce_norm_quant", h, self.peer, 0, C.c_uint64(L["out"].bias_ptr), x_in.ptr, C.c_int64(m), D, x_out.ptr,
+                   L["ln2"][0].ptr, L["ln2"][1].ptr, eps, self.hq.ptr, self.hq_scale.ptr)
+            x_in, x_out = x_out, x_in
+            L["ff1"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS_GELU, N.NS_BF16, self.ffh.ptr)
+            N.call("ns_quantize_rows_i8", h, self.ffh.ptr, N.NS_BF16, C.c_int64(m), self.ff_loc, self.hq.ptr, self.hq_scale.ptr)
+            L["ff2"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_NONE, N.NS_F32, self.peer_slots[1])
+            if i + 1 < len(self.layers):
+                g, bta = self.layers[i + 1]["ln1"]
+            elif head_from_last_rows:
+                g, bta = self.lnf
+            else:
+                g = bta = None
+            N.call("ns_tp_reduce_norm_quant", h, self.peer, 1, C.c_uint64(L["ff2"].bias_ptr), x_in.ptr, C.c_int64(m), D, x_out.ptr,
+                   g.ptr if g else 0, bta.ptr if bta else 0, eps, self.hq.ptr if g else 0, self.hq_scale.ptr if g else 0)
+            x_in, x_out = x_out, x_in
+            self._n += 10
+        if not head_from_last_rows:
+            N.call("ns_d2d_2d_async", h, C.c_uint64(self.last.ptr), C.c_uint64(D * 2), C.c_uint64(x_in.ptr + (steps - 1) * D * 2),
+                   C.c_uint64(steps * D * 2), C.c_uint64(D * 2), C.c_uint64(B))
+            N.call("ns_layernorm", h, C.c_uint64(self.last.ptr), N.NS_BF16, self.lnf[0].ptr, self.lnf[1].ptr, C.c_int64(B), D, eps, N.NS_I8,
+                   self.hq.ptr, self.hq_scale.ptr)
+            self._n += 2
+        self.head.forward(self.hq.ptr, self.hq_scale.ptr, B, N.EPI_BIAS, N.NS_F32, self.logits.ptr)
+        N.call("ns_argmax_partial", h, self.logits.ptr, B, self.v_loc, C.c_int64(self.v_loc), self.rank * self.v_loc, self.am_val.ptr, self.am_idx.ptr)
+        N.call("ns_allgather", h, self.comm, C.c_uint64(self.am_val.ptr), C.c_uint64(self.am_vals.ptr), C.c_int64(B), N.NS_F32)
+        N.call("ns_allgather", h, self.comm, C.c_uint64(self.am_idx.ptr), C.c_uint64(self.am_idxs.ptr), C.c_int64(B), N.NS_I32)
+        N.call("ns_argmax_merge", h, self.am_vals.ptr, self.am_idxs.ptr, self.tp, B, self.ids.ptr)
+        N.call("ns_add_i32", h, self.pos.ptr, steps)
+        self._n += 6
+        self.x = [x_in, x_out]
+
     # ------------------------------------------------------------------ generator (CharGpt.Generate, CharGpt.cs:231-318)
     def reset(self) -> None:
         """DecodingContext.Reset (Layers/Decoding.cs:84-92): position 0; stale cache rows stay masked."""
@@ -363,6 +431,13 @@ class GptW8A8:
         if self.graph is not None:
             self.dev.graph_destroy(self.graph)
             self.graph = None
+        if self.peer is not None:
+            # no rank may unmap its block while a peer's kernel can still read it
+            from . import dist
+            self.dev.synchronize()
+            dist.barrier()
+            N.call("ns_peer_group_destroy", self.peer)
+            self.peer = None
         for c in self.caches:
             N.call("ns_kv_cache_destroy", c)
         self.caches = []

@@ -86,6 +86,12 @@ SIGNATURES = {
     "ns_comm_async_error": [vp, P(i32)],
     "ns_comm_abort": [vp],
     "ns_comm_destroy": [vp],
+    "ns_peer_group_create": [vp, i32, i32, u64, P(vp)],
+    "ns_peer_group_handle": [vp, vp],
+    "ns_peer_group_connect": [vp, vp],
+    "ns_peer_group_slot": [vp, i32, P(u64)],
+    "ns_tp_reduce_norm_quant": [vp, vp, i32, u64, u64, i64, i32, u64, u64, u64, f32, u64, u64],
+    "ns_peer_group_destroy": [vp],
     "ns_f32_batched_matmul": [vp, u64, u64, u64, i32, i32, i32, i32, i32, i32, f32],
     "ns_f32_scale_mask_softmax": [vp, u64, u64, u64, i32, i32, i32, f32],
     "ns_f32_layernorm_fused": [vp, u64, u64, u64, u64, i32, i32, f32],

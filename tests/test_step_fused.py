@@ -136,3 +136,35 @@ def test_fused_and_unfused_decoder_agree(dev, orc):
     assert np.array_equal(out[0][0], out[1][0])
     assert np.array_equal(out[0][1].view(np.uint32), out[1][1].view(np.uint32))
 
+
+
+@pytest.mark.parametrize("M,NN", [(64, 2048), (5, 256), (200, 1024)])
+def test_peer_reduce_single_rank_equals_unfused(dev, orc, M, NN):
+    """ns_tp_reduce_norm_quant with one rank (the sum over ranks is the rank's own slot): bias + residual, LayerNorm and
+    quantisation must equal ns_bias_residual followed by ns_layernorm bit for bit, call after call (the epoch of a slot
+    advances on the device), and for both slots."""
+    group = C.c_void_p()
+    N.call("ns_peer_group_create", dev.handle, 0, 1, C.c_uint64(256 * 8192 * 4), C.byref(group))
+    bias = orc.normal((NN,), 31, 0.1)
+    gamma, beta = (1.0 + orc.normal((NN,), 32, 0.1)).astype(np.float32), orc.normal((NN,), 33, 0.1)
+    d_bias, d_g, d_b = dev.from_numpy(bias), dev.from_numpy(gamma), dev.from_numpy(beta)
+    for call in range(3):
+        slot = call & 1
+        part = orc.normal((M, NN), 40 + call)
+        res = orc.round_bf16(orc.normal((M, NN), 50 + call))
+        ptr = C.c_uint64()
+        N.call("ns_peer_group_slot", group, slot, C.byref(ptr))
+        N.call("ns_h2d", dev.handle, ptr, part.ctypes.data_as(C.c_void_p), C.c_uint64(part.nbytes))
+        d_part, d_res = dev.from_numpy(part), dev.from_numpy(res)
+        y_ref, q_ref, s_ref = dev.empty(M * NN, N.NS_BF16), dev.empty(M * NN, N.NS_I8), dev.empty(M)
+        N.call("ns_bias_residual", dev.handle, C.c_uint64(d_part.ptr), C.c_uint64(d_bias.ptr), C.c_uint64(d_res.ptr), N.NS_BF16, C.c_int64(M), NN,
+               N.NS_BF16, C.c_uint64(y_ref.ptr))
+        N.call("ns_layernorm", dev.handle, y_ref.ptr, N.NS_BF16, d_g.ptr, d_b.ptr, C.c_int64(M), NN, C.c_float(1e-5), N.NS_I8, q_ref.ptr, s_ref.ptr)
+        y, q, s = dev.empty(M * NN, N.NS_BF16), dev.empty(M * NN, N.NS_I8), dev.empty(M)
+        N.call("ns_tp_reduce_norm_quant", dev.handle, group, slot, C.c_uint64(d_bias.ptr), d_res.ptr, C.c_int64(M), NN, y.ptr, d_g.ptr, d_b.ptr,
+               C.c_float(1e-5), q.ptr, s.ptr)
+        dev.synchronize()
+        assert np.array_equal(y.download(), y_ref.download())
+        assert np.array_equal(q.download(), q_ref.download())
+        assert np.array_equal(s.download().view(np.uint32), s_ref.download().view(np.uint32))
+    N.call("ns_peer_group_destroy", group)

@@ -80,7 +80,16 @@ def gpu_mode():
             top2 = np.sort(ref.logit_trace[s][b])[-2:]
             assert top2[1] - top2[0] <= 2 * 5e-2 * max(1.0, abs(float(top2[1]))), \
                 f"sequence {b} leaves the oracle's tokens at step {s} without a near-tie (gap {top2[1] - top2[0]:.3g})"
+    assert m.peer is not None, "few-row passes must have used the peer-memory exchange"
     m.close()
+    # the same model over NCCL inside the layers (all-reduce, bias + residual, LayerNorm as three kernels) is held to the
+    # oracle in the same way (the peer-memory kernel adds the ranks' rows in rank order, NCCL in its own)
+    m2 = GptW8A8(dev, cfg, w, B, max_prefill=16, tp_rank=rank, tp_size=world, comm=comm, peer_exchange=False)
+    assert m2.peer is None
+    m2.prefill(prompt.astype(np.int32))
+    dev.synchronize()
+    assert orc.close(full, m2.read_logits(), 5e-2), orc.max_err(full, m2.read_logits())
+    m2.close()
     dist.barrier()
     print(f"rank {rank}: gpu ok, agreement {agree:.3f}")
 
