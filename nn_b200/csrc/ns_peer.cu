@@ -102,15 +102,22 @@ __global__ void ns_tp_reduce_norm_quant_kernel(const PeerReduceParams p)
             for (int j = 0; j < VPT; j++) {
                 const int col = ns_rows::vec_col(j);
                 const size_t idx = (size_t)r * p.cols + col;
-                float t[8];
-                {
-                    const float4 a = peer_load4(p.part[0] + idx), b = peer_load4(p.part[0] + idx + 4);
-                    t[0] = a.x; t[1] = a.y; t[2] = a.z; t[3] = a.w; t[4] = b.x; t[5] = b.y; t[6] = b.z; t[7] = b.w;
+                // every rank's vectors are requested before the first is used: one NVLink round trip, not one per rank
+                float4 va[PEER_MAX], vb[PEER_MAX];
+#pragma unroll
+                for (int k = 0; k < PEER_MAX; k++) {
+                    if (k < p.world) {
+                        va[k] = peer_load4(p.part[k] + idx);
+                        vb[k] = peer_load4(p.part[k] + idx + 4);
+                    }
                 }
-                for (int k = 1; k < p.world; k++) {
-                    const float4 a = peer_load4(p.part[k] + idx), b = peer_load4(p.part[k] + idx + 4);
-                    t[0] = __fadd_rn(t[0], a.x); t[1] = __fadd_rn(t[1], a.y); t[2] = __fadd_rn(t[2], a.z); t[3] = __fadd_rn(t[3], a.w);
-                    t[4] = __fadd_rn(t[4], b.x); t[5] = __fadd_rn(t[5], b.y); t[6] = __fadd_rn(t[6], b.z); t[7] = __fadd_rn(t[7], b.w);
+                float t[8] = {va[0].x, va[0].y, va[0].z, va[0].w, vb[0].x, vb[0].y, vb[0].z, vb[0].w};
+#pragma unroll
+                for (int k = 1; k < PEER_MAX; k++) {
+                    if (k < p.world) {
+                        t[0] = __fadd_rn(t[0], va[k].x); t[1] = __fadd_rn(t[1], va[k].y); t[2] = __fadd_rn(t[2], va[k].z); t[3] = __fadd_rn(t[3], va[k].w);
+                        t[4] = __fadd_rn(t[4], vb[k].x); t[5] = __fadd_rn(t[5], vb[k].y); t[6] = __fadd_rn(t[6], vb[k].z); t[7] = __fadd_rn(t[7], vb[k].w);
+                    }
                 }
                 if (p.bias != nullptr) {
                     const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col)), b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col + 4));
