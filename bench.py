@@ -282,13 +282,15 @@ def run_case(spec: str):
       attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
       gpt_decode:LAYERS       the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64)
                               cut to LAYERS layers: prompt of 512, then three decoding steps (seeded numpy weights);
-                              prints the device time of a replayed step
+                              prints the device time of a replayed step.  Under `python -m torch.distributed.run
+                              --nproc-per-node N` the decoder is tensor-parallel over N GPUs (one rank per GPU, the
+                              slowest rank's time is printed by rank 0)
     """
     import numpy as np
     from nn_b200 import native as N
     from nn_b200.device import Device
     name, _, arg = spec.partition(":")
-    dev = Device(0)
+    dev = Device(int(os.environ.get("LOCAL_RANK", "0")) if name == "gpt_decode" else 0)
     if name == "qmatmul_i8":
         m = int(arg or M)
         a, w = dev.empty(m * K, N.NS_I8), dev.empty(NN * K, N.NS_I8)
@@ -347,7 +349,10 @@ def run_case(spec: str):
              "l0.ln1_g": 1.0 + nrm(D, s=0.05), "l0.ln1_b": nrm(D), "l0.ln2_g": 1.0 + nrm(D, s=0.05), "l0.ln2_b": nrm(D),
              "l0.qkv_w": nrm(D, 3 * D), "l0.qkv_b": nrm(3 * D, s=0.01), "l0.out_w": nrm(D, D), "l0.out_b": nrm(D, s=0.01),
              "l0.ff1_w": nrm(D, FF), "l0.ff1_b": nrm(FF, s=0.01), "l0.ff2_w": nrm(FF, D), "l0.ff2_b": nrm(D, s=0.01)}
-        model = GptW8A8(dev, cfg, w, B, max_prefill=prompt_len, share_layer_weights=True)   # every layer its own device copy
+        from nn_b200 import dist
+        comm, rank, world = dist.init_comm(dev)
+        model = GptW8A8(dev, cfg, w, B, max_prefill=prompt_len, share_layer_weights=True, tp_rank=rank, tp_size=world,
+                        comm=comm)   # every layer its own device copy
         model.prefill(rng.integers(0, V, (B, prompt_len)).astype(np.int32))
         for _ in range(3):
             model.step(False)
@@ -359,8 +364,13 @@ def run_case(spec: str):
         for _ in range(20):
             model.step(True)
         dev.record(e1)
-        ms = dev.elapsed_ms(e0, e1) / 20
-        print(json.dumps({"case": spec, "ok": True, "ms_per_replayed_step": ms, "tokens_per_s": B / ms * 1e3, "layers": layers}))
+        ms = dist.all_reduce_max(dev.elapsed_ms(e0, e1) / 20)
+        dev.synchronize()
+        launches = model.launches_per_step
+        model.close()
+        if rank == 0:
+            print(json.dumps({"case": spec, "ok": True, "ms_per_replayed_step": ms, "tokens_per_s": B / ms * 1e3, "layers": layers,
+                              "tensor_parallel": world, "launches_per_step": launches}))
         return
     else:
         raise SystemExit(f"unknown case {spec}")
