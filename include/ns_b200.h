@@ -352,6 +352,8 @@ NS_API int ns_comm_destroy(ns_comm_t comm);
  * multi-GPU code (Tensor.To goes through a host array, Tensor.cs:244-253). */
 NS_API int ns_peer_group_create(ns_device_t dev, int rank, int world, uint64_t slot_bytes, ns_peer_group_t* group);
 NS_API int ns_peer_group_handle(ns_peer_group_t group, void* handle64);
+/* handles: world x 64 bytes in rank order.  Null: the other ranks become stand-ins that never arrive (a test of the bounded
+ * wait on one GPU: the next ns_tp_reduce_norm_quant gives up after about a second with status 400 + the missing rank). */
 NS_API int ns_peer_group_connect(ns_peer_group_t group, const void* handles);
 /* Device address of this rank's slot (0 or 1): the row-parallel product writes its float partial rows [rows, cols] there. */
 NS_API int ns_peer_group_slot(ns_peer_group_t group, int slot, uint64_t* ptr);

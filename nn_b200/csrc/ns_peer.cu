@@ -38,6 +38,7 @@ struct NsPeerGroup {
     uint8_t* peers[PEER_MAX] = {nullptr};        // every rank's block as mapped here (peers[rank] == local)
     uint32_t* state = nullptr;                   // local only: epoch[PEER_SLOTS], ticket[PEER_SLOTS]
     bool connected = false;
+    bool loopback = false;                       // peers are stand-ins mapped to the local block
 };
 
 struct PeerReduceParams {
@@ -201,11 +202,18 @@ extern "C" int ns_peer_group_handle(ns_peer_group_t h, void* handle64)
 extern "C" int ns_peer_group_connect(ns_peer_group_t h, const void* handles)
 {
     NsPeerGroup* g = as_group(h);
-    NS_REQUIRE(g != nullptr && handles != nullptr, NS_ERR_ARGUMENT, "ns_peer_group_connect: null argument");
+    NS_REQUIRE(g != nullptr, NS_ERR_ARGUMENT, "ns_peer_group_connect: null argument");
     int rc = ns_device_make_current(g->dev);
     if (rc != NS_OK) return rc;
     for (int r = 0; r < g->world; r++) {
         if (r == g->rank || g->peers[r] != nullptr) continue;
+        if (handles == nullptr) {
+            // no handles: the other ranks are stand-ins that never arrive (their flag words are never written); this is
+            // how the bounded wait is exercised on one GPU
+            g->peers[r] = g->local;
+            g->loopback = true;
+            continue;
+        }
         cudaIpcMemHandle_t ipc;
         memcpy(&ipc, reinterpret_cast<const uint8_t*>(handles) + 64 * r, 64);
         void* ptr = nullptr;
@@ -276,7 +284,7 @@ extern "C" int ns_peer_group_destroy(ns_peer_group_t h)
     ns_device_make_current(g->dev);
     cudaStreamSynchronize(g->dev->stream);
     for (int r = 0; r < g->world; r++)
-        if (r != g->rank && g->peers[r] != nullptr) cudaIpcCloseMemHandle(g->peers[r]);
+        if (r != g->rank && g->peers[r] != nullptr && !g->loopback) cudaIpcCloseMemHandle(g->peers[r]);
     if (g->local) cudaFree(g->local);
     if (g->state) cudaFree(g->state);
     delete g;

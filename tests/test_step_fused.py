@@ -168,3 +168,31 @@ def test_peer_reduce_single_rank_equals_unfused(dev, orc, M, NN):
         assert np.array_equal(q.download(), q_ref.download())
         assert np.array_equal(s.download().view(np.uint32), s_ref.download().view(np.uint32))
     N.call("ns_peer_group_destroy", group)
+
+
+def test_peer_reduce_gives_up_when_a_rank_never_arrives(dev, orc):
+    """Failure detection without a GPU fault: a group of two whose second rank is a stand-in that never signals.  The
+    kernel's wait runs out (about a second), the next synchronisation reports NS_ERR_KERNEL with status 400 + the missing
+    rank, and the device stays usable: a complete group of one works right afterwards."""
+    M, NN = 8, 256
+    group = C.c_void_p()
+    N.call("ns_peer_group_create", dev.handle, 0, 2, C.c_uint64(256 * 1024), C.byref(group))
+    N.call("ns_peer_group_connect", group, None)
+    y = dev.zeros(M * NN, N.NS_BF16)
+    N.call("ns_tp_reduce_norm_quant", dev.handle, group, 0, C.c_uint64(0), 0, C.c_int64(M), NN, y.ptr, 0, 0, C.c_float(1e-5), 0, 0)
+    with pytest.raises(N.NsError) as err:
+        dev.synchronize()
+    assert "status 401" in str(err.value)
+    assert not y.download().any(), "no row may be written when a rank is missing"
+    N.call("ns_peer_group_destroy", group)
+    # the device is still usable
+    solo = C.c_void_p()
+    N.call("ns_peer_group_create", dev.handle, 0, 1, C.c_uint64(256 * 1024), C.byref(solo))
+    part = orc.normal((M, NN), 3)
+    ptr = C.c_uint64()
+    N.call("ns_peer_group_slot", solo, 0, C.byref(ptr))
+    N.call("ns_h2d", dev.handle, ptr, part.ctypes.data_as(C.c_void_p), C.c_uint64(part.nbytes))
+    N.call("ns_tp_reduce_norm_quant", dev.handle, solo, 0, C.c_uint64(0), 0, C.c_int64(M), NN, y.ptr, 0, 0, C.c_float(1e-5), 0, 0)
+    dev.synchronize()
+    assert np.array_equal(y.download((M, NN)), orc.round_bf16(part))
+    N.call("ns_peer_group_destroy", solo)
