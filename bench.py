@@ -270,7 +270,7 @@ def run_ours(args, rank, world, local_rank):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
 # in profiles/.
-TRAFFIC_BYTES_PER_LAUNCH = 145519104  # 62.24 MB read + 83.28 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
+TRAFFIC_BYTES_PER_LAUNCH = 149024512  # 63.85 MB read + 85.18 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
 
 
 def run_case(spec: str):
