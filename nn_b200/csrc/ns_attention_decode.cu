@@ -69,13 +69,14 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8])
 // One CTA per (batch, head, new position, split).  DH = head_dim.  LPR = DH / 32 lanes share one cached row, each
 // lane owning four 16-byte pieces of it (piece i of lane `sub` is piece sub + LPR * i of the row, so the lanes of a
 // row read contiguous 16 * LPR bytes per load).
-template <int DH>
+template <int DH, int U>
 __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const DecodeParams p)
 {
     constexpr int LPR = DH / 32;               // lanes per cached row
     constexpr int RPW = 32 / LPR;              // rows per warp per load round
     constexpr int GROUPS = DEC_THREADS / LPR;  // rows in flight per CTA
-    constexpr int U = 2;                       // load rounds in flight
+    // U = load rounds in flight per lane (a round = one cached row per lane group): two when thousands of CTAs share the
+    // SMs, four when the grid is small and a CTA's own chain of loads is what its time consists of
     __shared__ float s_scores[DEC_CHUNK];
     __shared__ float s_red[DEC_THREADS / 32];
     __shared__ float s_acc[GROUPS][DH];
@@ -286,7 +287,10 @@ template <int DH>
 int launch_decode(NsDevice* d, const DecodeParams& p)
 {
     const int rows = p.batch * p.heads * p.steps;
-    NS_CUDA(ns_launch_plain(ns_attention_decode_kernel<DH>, dim3(rows * p.splits), dim3(DEC_THREADS), 0, d->stream, p));
+    if ((int64_t)rows * p.splits < 3 * (int64_t)d->sm_count)   // measured: 384 CTAs gain 9 %, 512 CTAs lose 30 % with four rounds
+        NS_CUDA(ns_launch_plain(ns_attention_decode_kernel<DH, 4>, dim3(rows * p.splits), dim3(DEC_THREADS), 0, d->stream, p));
+    else
+        NS_CUDA(ns_launch_plain(ns_attention_decode_kernel<DH, 2>, dim3(rows * p.splits), dim3(DEC_THREADS), 0, d->stream, p));
     if (p.splits > 1) {
         NS_CUDA(ns_launch_plain(ns_attention_combine_kernel<DH>, dim3(rows), dim3(DH < 64 ? 32 : 64), 0, d->stream, p));
     }
