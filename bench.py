@@ -1,17 +1,23 @@
-"""Benchmark of the hot path: int8 QuantizedMatMul (int8 x int8 -> int32, per-channel dequant + bias epilogue).
+"""Benchmark of the hot path: int8 QuantizedMatMul (int8 x int8 -> int32, per-channel dequant + bias epilogue), and the
+int8 GPT decoder's greedy generation (tokens/s), tensor-parallel over the GPUs of the run.
 
-Workload (benchmark configuration "int8 QuantizedMatMul sweep", the largest M): A [8192, 4096] float ~N(0,1) quantised per
-row, W [4096, 4096] ~N(0,0.02) quantised per output channel, bias ~N(0,0.01), float output.  One step = one pass
-of the product over one batch of 8192 rows.  With N > 1 GPUs every rank runs its own batch of rows against its own
-copy of the weights (batch sharding, no data-path collective): weak scaling.
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-gpt]
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+Headline workload (benchmark configuration "int8 QuantizedMatMul sweep", the largest M): A [8192, 4096] float ~N(0,1)
+quantised per row, W [4096, 4096] ~N(0,0.02) quantised per output channel, bias ~N(0,0.01), float output.  One step =
+one pass of the product over one batch of 8192 rows.  With N > 1 GPUs every rank runs its own batch of rows against
+its own copy of the weights (batch sharding, no data-path collective): weak scaling.
 
-Prints ONE JSON line (rank 0).  `value` is device-resident throughput, `e2e` is the same product through the C
-ABI from pinned host buffers (float activations in, float result out, copies inside the timed region), `roofline`
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput, `e2e` is the same product through the C ABI
+from pinned host buffers (float activations in, float result out, copies inside the timed region), `roofline`
 compares the tcgen05 kernel with the tensor-core peak, `cpu_baseline` times the oracle's restatement of the
-reference's CPU product on this host's cores.  `--impl reference` times that CPU restatement alone (the reference
-is C#/.NET and cannot run here).
+reference's CPU product on this host's cores.  `gpt_decode` is the second half of the metric: the 24-layer int8
+decoder (d 2048, 16 heads, FF 8192, vocabulary 32000), batch 64, prompt 512, 256 greedy tokens, tensor-parallel over
+the N ranks, after a 40-token warm-up generation (the reference's harness does the same:
+samples/NeuralSharp.Samples.Transformer/Program.cs:122-142; tokens/s over all sequences, samples/Shared/Gpt/
+CharGpt.cs:321-333); on rank 0 the same model also runs on one GPU and the tokens are compared.
+`--impl reference` times the CPU restatement alone (the reference is C#/.NET and cannot run here).
 """
 from __future__ import annotations
 
@@ -23,6 +29,7 @@ import statistics
 import subprocess
 import sys
 import time
+import zlib
 
 import numpy as np
 
@@ -33,9 +40,15 @@ M, K, NN = 8192, 4096, 4096
 OPS = 2.0 * M * K * NN
 ALGO_BYTES = NN * K + M * K + 4 * M * NN + 4 * (M + 2 * NN)
 METRIC, UNIT = "int8_quantized_matmul_tops", "TOPS"
+MIN_TIMED_SECONDS = 0.35      # the timed region is stretched to at least this (a 200 ms clock sampler must see it)
 CONFIG = {"workload": "int8 QuantizedMatMul M=8192 K=4096 N=4096 (per-row A scales, per-channel W scales, bias, f32 out)",
           "l2": "4 operand/result sets rotated per step (704 MB footprint > 126 MB L2)", "seed": 1,
-          "clocks_window": "nvidia-smi sampled every 200 ms over ~1 s of back-to-back steps that contains the timed region"}
+          "clocks_window": "nvidia-smi sampled every 200 ms over the loaded region: 0.45 s of untimed steps, the timed steps "
+                           "(at least 0.35 s), 0.45 s of untimed steps"}
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
+# in profiles/.
+TRAFFIC_BYTES_PER_LAUNCH = 149024512  # 63.85 MB read + 85.18 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
 
 
 def measured_peaks():
@@ -52,8 +65,8 @@ class ClockSampler:
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.gpu_index, self.proc, self.path = gpu_index, None, f"/tmp/ns_b200_clocks_{os.getpid()}.csv"
+    def __init__(self, gpu_index: int, tag: str = ""):
+        self.gpu_index, self.proc, self.path = gpu_index, None, f"/tmp/ns_b200_clocks_{os.getpid()}{tag}.csv"
 
     def start(self):
         try:
@@ -126,6 +139,189 @@ def run_reference(args, rank):
                       "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# the decoder of benchmark configuration 5
+# ---------------------------------------------------------------------------------------------------------------
+GPT = {"vocab": 32000, "dim": 2048, "heads": 16, "layers": 24, "ff_dim": 8192, "batch": 64, "prompt": 512, "new_tokens": 256,
+       "warmup_tokens": 40, "seed": 4}
+
+
+class SyntheticGptWeights(dict):
+    """The weight mapping GptW8A8 takes, produced tensor by tensor on first use and not kept: matrices ~N(0, 0.02)
+    (the benchmark configuration's rule), LayerNorm gains 1 + N(0, 0.05), biases N(0, 0.01).  The stream of a tensor depends on
+    (seed, its key) only, so every rank of a tensor-parallel run cuts its shards from identical matrices."""
+
+    def __init__(self, cfg, seed: int):
+        super().__init__()
+        self.cfg, self.seed = cfg, seed
+
+    def _shape(self, name: str):
+        c = self.cfg
+        D, FF, V = c.dim, c.ff_dim, c.vocab
+        table = {"tok": (V, D), "pos": (c.context, D), "lnf_g": (D,), "lnf_b": (D,), "head_w": (D, V), "head_b": (V,),
+                 "ln1_g": (D,), "ln1_b": (D,), "ln2_g": (D,), "ln2_b": (D,), "qkv_w": (D, 3 * D), "qkv_b": (3 * D,), "out_w": (D, D),
+                 "out_b": (D,), "ff1_w": (D, FF), "ff1_b": (FF,), "ff2_w": (FF, D), "ff2_b": (D,)}
+        return table[name]
+
+    def __getitem__(self, key: str):
+        name = key.split(".")[-1]
+        shape = self._shape(name)
+        rng = np.random.default_rng([self.seed, zlib.crc32(key.encode())])
+        x = rng.standard_normal(shape, dtype=np.float32)
+        if name.endswith("_g"):
+            x *= 0.05
+            x += 1.0
+        elif name.endswith("_b") and len(shape) == 1 and name not in ("ln1_b", "ln2_b", "lnf_b"):
+            x *= 0.01
+        else:
+            x *= 0.02
+        return x
+
+
+def gpt_prompt(cfg, batch: int, length: int, seed: int) -> np.ndarray:
+    return np.random.default_rng([seed, 7]).integers(0, cfg.vocab, (batch, length)).astype(np.int32)
+
+
+def decode_step_bytes(cfg, batch: int, context: float, gpus: int) -> float:
+    """Algorithmic HBM bytes of one decoding step per GPU: int8 weights of every Linear once + the cached keys and values
+    of `context` positions (bf16), both sharded over the GPUs."""
+    D, FF, V, L = cfg.dim, cfg.ff_dim, cfg.vocab, cfg.layers
+    weights = L * (D * 3 * D + D * D + 2 * D * FF) + D * V
+    kv = L * 2 * batch * context * D * 2
+    return (weights + kv) / gpus
+
+
+def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tokens: int, compare_tp1: bool):
+    """Builds the decoder tensor-parallel over the ranks of the run, warms up, times one generation; returns the
+    `gpt_decode` record on rank 0 (None elsewhere)."""
+    from nn_b200 import dist as nsdist
+    from nn_b200.gpt import GptConfig, GptW8A8
+
+    g = GPT
+    B, P = g["batch"], g["prompt"]
+    cfg = GptConfig(vocab=g["vocab"], dim=g["dim"], heads=g["heads"], layers=layers, ff_dim=g["ff_dim"], context=P + g["new_tokens"])
+    weights = SyntheticGptWeights(cfg, g["seed"])
+    prompt = gpt_prompt(cfg, B, P, g["seed"])
+    comm = None
+    if world > 1:
+        comm, _, _ = nsdist.init_comm(dev)
+    t0 = time.perf_counter()
+    model = GptW8A8(dev, cfg, weights, B, max_prefill=P, tp_rank=rank, tp_size=world, comm=comm)
+    build_s = time.perf_counter() - t0
+
+    model.generate(prompt, min(g["warmup_tokens"], new_tokens))       # warm-up generation: sizes scratch, records the step graph
+    dev.synchronize()
+    nsdist.barrier()
+    sampler = ClockSampler(dev.ordinal, "_gpt")
+    if rank == 0:
+        sampler.start()
+    marks = {}
+    wall0 = time.perf_counter()
+    tokens, resets = model.generate(prompt, new_tokens, marks=marks)
+    dev.synchronize()
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop() if rank == 0 else None
+    prefill_ms = nsdist.all_reduce_max(dev.elapsed_ms(marks["start"], marks["prefill_end"]))
+    steps = marks["steps"]
+    decode_ms = nsdist.all_reduce_max(dev.elapsed_ms(marks["prefill_end"], steps[-1][1]))
+    n_steps = new_tokens - 1
+    seg = []
+    prev_count, prev_event = 1, marks["prefill_end"]
+    for count, ev in steps:
+        seg.append((prev_count, count, nsdist.all_reduce_max(dev.elapsed_ms(prev_event, ev)) / max(1, count - prev_count)))
+        prev_count, prev_event = count, ev
+    ms_step = decode_ms / n_steps
+    launches = model.launches_per_step
+
+    # the step with the cross-GPU exchange in its single-rank form (results are not the model's): what the exchange costs
+    exchange = None
+    if world > 1 and model.peer is not None:
+        def replay_ms(n=48):
+            model.prefill(prompt)
+            for _ in range(3):
+                model.step(True)
+            e0, e1 = dev.event(), dev.event()
+            dev.synchronize()
+            nsdist.barrier()
+            dev.record(e0)
+            for _ in range(n):
+                model.step(True)
+            dev.record(e1)
+            return nsdist.all_reduce_max(dev.elapsed_ms(e0, e1) / n)
+        full = replay_ms()
+        model.set_local_exchange(True)
+        local = replay_ms()
+        model.set_local_exchange(False)
+        exchange = {"ms_per_step_full": full, "ms_per_step_single_rank_exchange": local, "exchange_ms_per_step": full - local,
+                    "context": f"{P}+3..{P}+51"}
+    model.close()
+    nsdist.barrier()
+
+    # the same model on one GPU (rank 0), tokens compared step by step
+    compare = None
+    if rank == 0:
+        if world == 1:
+            compare = {"tokens_equal_tp1_prefix": new_tokens, "note": "this run is the one-GPU model"}
+        elif compare_tp1:
+            one = GptW8A8(dev, cfg, weights, B, max_prefill=P)
+            ref_tokens, _ = one.generate(prompt, new_tokens)
+            same = np.all(ref_tokens == tokens, axis=0)
+            prefix = int(np.argmin(same)) if not same.all() else new_tokens
+            compare = {"tokens_equal_tp1_prefix": prefix, "of_steps": new_tokens,
+                       "sequences_equal_throughout": int(np.all(ref_tokens == tokens, axis=1).sum()), "of_sequences": B}
+            if prefix < new_tokens:
+                b = int(np.argmax(ref_tokens[:, prefix] != tokens[:, prefix]))
+                one.generate(prompt, prefix + 1)                       # deterministic: ends on the step that produced token `prefix`
+                dev.synchronize()
+                row = one.read_logits()[b]
+                top = np.sort(row)[-2:]
+                tol = 2 * 5e-2 * max(1.0, abs(float(top[1])))
+                compare["first_departure"] = {"step": prefix, "sequence": b, "tp1_token": int(ref_tokens[b, prefix]), "tpN_token": int(tokens[b, prefix]),
+                                              "tp1_top2_gap": float(top[1] - top[0]), "near_tie_tolerance": tol,
+                                              "is_near_tie": bool(top[1] - top[0] <= tol),
+                                              "tpN_token_logit_below_top": float(top[1] - row[int(tokens[b, prefix])])}
+            one.close()
+    nsdist.barrier()
+    if rank != 0:
+        return None
+    mean_ctx = P + (new_tokens / 2.0)
+    step_bytes = decode_step_bytes(cfg, B, mean_ctx, world)
+    rec = {"config": {"model": f"int8 GPT decoder, {layers} layers, d {cfg.dim}, {cfg.heads} heads, ff {cfg.ff_dim}, vocabulary {cfg.vocab}",
+                      "batch": B, "prompt": P, "new_tokens": new_tokens, "warmup_tokens": min(g["warmup_tokens"], new_tokens),
+                      "parallelism": f"tp{world}" if world > 1 else "1 gpu",
+                      "weights": "synthetic, seeded per tensor, every layer its own values", "seed": g["seed"]},
+           "tokens_per_s": B * n_steps / (decode_ms * 1e-3), "tokens_per_s_wall_incl_prefill": B * new_tokens / wall,
+           "prefill_ms": prefill_ms, "prefill_tokens_per_s": B * P / (prefill_ms * 1e-3), "decode_ms": decode_ms, "ms_per_step": ms_step,
+           "ms_per_step_first_segment": seg[0][2], "ms_per_step_last_segment": seg[-1][2],
+           "segments": [{"tokens": [a, b], "ms_per_step": ms} for a, b, ms in seg],
+           "launches_per_step": launches, "context_resets": resets,
+           "hbm_bytes_per_step_per_gpu": step_bytes, "hbm_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm"],
+           "hbm_peak_gbs": peaks["hbm"], "clocks": clocks, "model_build_s": build_s, "exchange": exchange}
+    if compare is not None:
+        rec.update(compare)
+    return rec
+
+
+def bind_near_gpu(gpu_index: int):
+    """Restricts this process to the host cores NVML lists as local to the GPU (when that is a proper subset of what it may
+    use), so that pinned buffers allocated next land on the GPU's NUMA node.  Returns (old affinity, note)."""
+    old = os.sched_getaffinity(0)
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        near = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        pynvml.nvmlShutdown()
+    except Exception as e:   # NVML missing or not permitted: stay as we are
+        return old, f"NVML affinity unavailable ({type(e).__name__})"
+    both = near & old
+    if both and both != old:
+        os.sched_setaffinity(0, both)
+        return old, f"bound to {len(both)} GPU-local cores of {len(old)}"
+    return old, f"GPU-local cores = all {len(old)} usable cores (one NUMA node visible)"
+
+
 def run_ours(args, rank, world, local_rank):
     from nn_b200 import native as N
     from nn_b200.device import Device
@@ -135,9 +331,29 @@ def run_ours(args, rank, world, local_rank):
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # gloo for host-side rendezvous (NCCL ids, IPC handles), NCCL for barriers and the max over ranks
+        dist.init_process_group("cpu:gloo,cuda:nccl", device_id=torch.device("cuda", local_rank))
     dev = Device(local_rank)
     peaks = measured_peaks()
+
+    def barrier():
+        dev.synchronize()
+        if dist is not None:
+            import torch
+            t = torch.zeros(1, device=f"cuda:{local_rank}")
+            dist.all_reduce(t)
+            torch.cuda.synchronize()
+        dev.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], device=f"cuda:{local_rank}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    barrier()      # throw-away: the first collective sets up the communicator; later barriers take microseconds
 
     # ---- operands resident in HBM: SETS rotating sets, generated and quantised on the device
     SETS = 4
@@ -155,18 +371,14 @@ def run_ours(args, rank, world, local_rank):
         y = dev.empty(M * NN)
         dev.synchronize()
         w.release()
+        if s > 0:
+            x.release()
         sets.append({"x": x, "xq": xq, "xs": xs, "wq": wq, "ws": ws, "bias": bias, "y": y})
 
     def step(i):
         t = sets[i % SETS]
         N.call("ns_qmatmul_i8", dev.handle, t["xq"].ptr, t["xs"].ptr, t["wq"].ptr, t["ws"].ptr, t["bias"].ptr, 0, 0, M, NN, K,
                N.EPI_BIAS, N.NS_F32, t["y"].ptr, 0)
-
-    def barrier():
-        dev.synchronize()
-        if dist is not None:
-            dist.barrier()
-        dev.synchronize()
 
     def load_for(seconds):
         # untimed steps of the same workload, so that clock samples (every 200 ms) bracket the timed region
@@ -177,9 +389,19 @@ def run_ours(args, rank, world, local_rank):
                 dev.synchronize()
         dev.synchronize()
 
+    e0, e1 = dev.event(), dev.event()
     for i in range(args.warmup):
         step(i)
-    e0, e1 = dev.event(), dev.event()
+    # a first estimate of the step time sizes the timed region: the K steps asked for, and as many more as it takes
+    # for the region to last MIN_TIMED_SECONDS
+    dev.synchronize()
+    dev.record(e0)
+    for i in range(20):
+        step(i)
+    dev.record(e1)
+    est_ms = max(dev.elapsed_ms(e0, e1) / 20, 1e-3)
+    executed = max(args.steps, int(MIN_TIMED_SECONDS * 1e3 / est_ms) + 1)
+    executed = int(max_over_ranks(float(executed)))
     sampler = ClockSampler(local_rank)
     dev.synchronize()
     if rank == 0:
@@ -187,23 +409,38 @@ def run_ours(args, rank, world, local_rank):
     load_for(0.45)
     barrier()
     dev.record(e0)
-    for i in range(args.steps):
+    for i in range(executed):
         step(i)
     dev.record(e1)
     ms_total = dev.elapsed_ms(e0, e1)
     barrier()
     load_for(0.45)
     clocks = sampler.stop() if rank == 0 else None
-    if dist is not None:
-        import torch
-        t = torch.tensor([ms_total], device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+    ms_total = max_over_ranks(ms_total)
+    ms_step = ms_total / executed
     value = world * OPS / (ms_step * 1e-3) / 1e12
+
+    # ---- the main loop alone (loads + MMAs of the same pair kernel, nothing dequantised or written), K = 16384: the int8
+    # rate this library's pipeline reaches, as a measured yardstick beside 2 x the cuBLAS bf16 figure
+    KP = 16384
+    pa, pw = dev.empty(M * KP, N.NS_I8), dev.empty(NN * KP, N.NS_I8)
+    N.call("ns_fill_normal", dev.handle, pa.ptr, N.NS_I8, C.c_int64(M * KP), 21, 0.0, 40.0)
+    N.call("ns_fill_normal", dev.handle, pw.ptr, N.NS_I8, C.c_int64(NN * KP), 22, 0.0, 40.0)
+    for _ in range(3):
+        N.call("ns_bench_i8_mainloop", dev.handle, pa.ptr, pw.ptr, M, NN, KP)
+    n_proxy = 200
+    barrier()
+    dev.record(e0)
+    for _ in range(n_proxy):
+        N.call("ns_bench_i8_mainloop", dev.handle, pa.ptr, pw.ptr, M, NN, KP)
+    dev.record(e1)
+    proxy_tops = 2.0 * M * KP * NN / (dev.elapsed_ms(e0, e1) / n_proxy * 1e-3) / 1e12
+    barrier()
+    pa.release(); pw.release()
 
     # ---- end to end: pinned host float activations in, float result out, through the C ABI
     e2e_steps = max(3, min(args.steps, 8))
+    old_affinity, affinity_note = bind_near_gpu(local_rank)
     hx, hy = C.c_void_p(), C.c_void_p()
     N.call("ns_host_alloc", C.c_uint64(M * K * 4), C.byref(hx))
     N.call("ns_host_alloc", C.c_uint64(M * NN * 4), C.byref(hy))
@@ -232,32 +469,61 @@ def run_ours(args, rank, world, local_rank):
     dev.record(e1)
     e2e_ms = dev.elapsed_ms(e0, e1) / e2e_steps
     barrier()
-    if dist is not None:
-        import torch
-        t2 = torch.tensor([e2e_ms], device=f"cuda:{local_rank}")
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t2.item())
+    e2e_ms = max_over_ranks(e2e_ms)
+    # the host link alone, every rank at once: uploads of the same pinned buffer, nothing else
+    barrier()
+    dev.record(e0)
+    for i in range(4):
+        N.call("ns_h2d_async", dev.handle, C.c_uint64(t["x"].ptr), hx, C.c_uint64(M * K * 4))
+    dev.record(e1)
+    h2d_ms = max_over_ranks(dev.elapsed_ms(e0, e1) / 4)
+    barrier()
+    os.sched_setaffinity(0, old_affinity)
     e2e = {"value": world * OPS / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * NN * 4,
            "ms_per_step": e2e_ms, "steps": e2e_steps, "call": "ns_linear_forward_host (pinned float32 host buffers, three-stream row pipeline)",
-           "link_gbs_each_way": M * K * 4 / (e2e_ms * 1e-3) / 1e9}
+           "link_gbs_each_way": M * K * 4 / (e2e_ms * 1e-3) / 1e9,
+           "h2d_alone_gbs_per_gpu": M * K * 4 / (h2d_ms * 1e-3) / 1e9, "h2d_alone_gbs_all_gpus": world * M * K * 4 / (h2d_ms * 1e-3) / 1e9,
+           "host_affinity": affinity_note}
+    N.call("ns_linear_destroy", lin)
+    N.call("ns_host_free", hx)
+    N.call("ns_host_free", hy)
+    for tset in sets:
+        for st in tset.values():
+            st.release()
+    sets.clear()
+
+    # ---- the decoder: tokens/s of a greedy generation, tensor-parallel over the ranks
+    gpt = None
+    if not args.no_gpt:
+        gpt = run_gpt_decode(dev, rank, world, peaks, args.gpt_layers, args.gpt_tokens, compare_tp1=not args.no_tp1)
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
     achieved = OPS / (ms_step * 1e-3) / 1e12
-    # The timed steps run inside about a second of back-to-back products (the clocks window), under the power cap:
-    # the sustained figure is the denominator; the burst one and the nominal one are given beside it.
-    int8_peak = 2.0 * peaks["bf16_sustained"]
+    # Denominator: MEASURED_PEAKS.json has no int8 figure, so 2 x the cuBLAS bf16 rate.  Its burst figure was taken at the
+    # clock a tensor-core load holds for a short while (~1.45 GHz), the sustained one at ~1.35 GHz under the power cap:
+    # the line's own median SM clock says which regime the timed steps ran in.
+    sm = clocks.get("sm_mhz") if clocks else None
+    use_sustained = sm is not None and sm <= 1380.0
+    int8_peak = 2.0 * (peaks["bf16_sustained"] if use_sustained else peaks["bf16"])
     roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s", "frac": achieved / int8_peak,
                 "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "ns_gemm_pair_kernel<int8> (256 x 256 tiles, tcgen05 cta_group::2)",
-                "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}; a kernel timed inside a long "
-                               "loaded region, SM clock in `clocks`); that file has no int8 figure; nominal dense int8 is 4500",
-                "frac_of_burst": achieved / (2.0 * peaks["bf16"]), "frac_of_nominal_4500": achieved / 4500.0,
+                "peak_source": ("2 x bf16_tflops_sustained" if use_sustained else "2 x bf16_tflops (burst)") +
+                               f" of MEASURED_PEAKS.json ({peaks['source']}): median SM clock of the loaded region {sm} MHz "
+                               + ("<= 1380" if use_sustained else "> 1380") + "; that file has no int8 figure; nominal dense int8 is 4500",
+                "frac_of_burst": achieved / (2.0 * peaks["bf16"]), "frac_of_sustained": achieved / (2.0 * peaks["bf16_sustained"]),
+                "frac_of_nominal_4500": achieved / 4500.0,
+                "i8_mainloop_proxy_tops": proxy_tops, "frac_of_i8_proxy": achieved / proxy_tops,
+                "i8_mainloop_proxy": f"ns_bench_i8_mainloop M={M} N={NN} K={KP}, {n_proxy} launches: loads + MMAs only, nothing written",
                 "algorithmic_bytes": ALGO_BYTES, "hbm_gbs_at_this_rate": ALGO_BYTES / (ms_step * 1e-3) / 1e9}
-    out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+    out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "steps_executed": executed,
+           "timed_region_s": ms_total * 1e-3, "warmup": args.warmup,
            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i8",
-           "data": "synthetic", "config": CONFIG, "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps, "roofline": roofline}
+           "data": "synthetic", "config": CONFIG, "clocks": clocks, "e2e": e2e, "gpu_launches": executed, "roofline": roofline}
+    if gpt is not None:
+        out["gpt_decode"] = gpt
     if world == 1:
         tops, cores, secs = cpu_reference_tops(4096, 2)
         out["cpu_baseline"] = {"value": tops, "unit": UNIT, "cores": cores, "kind": "port",
@@ -268,25 +534,20 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
-# in profiles/.
-TRAFFIC_BYTES_PER_LAUNCH = 149024512  # 63.85 MB read + 85.18 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
-
-
 def run_case(spec: str):
     """Small fixed cases for profiler captures (`ncu ... python bench.py --case NAME:ARGS`): three launches of one
-    kernel on device-generated inputs, nothing timed.
+    kernel on device-generated inputs, nothing timed unless stated.
       qmatmul_i8:M            int8 product, K = N = 4096, bias epilogue, f32 out
       qmatmul_i8_rows:M       int8 product of M <= 8 rows with 32768 x 8192 weights (268 MB, beyond L2): the row-streaming kernel
+      i8_mainloop_peak[:K]    the pair kernel's main loop alone (ns_bench_i8_mainloop), M = 8192, N = 4096, K = 16384 unless given:
+                              prints the TOPS of 200 timed launches -- the int8 tensor-core rate the load / MMA pipeline reaches
       attention_decode:L      batch 64, 32 heads, head_dim 128, cache length L
       attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
-      gpt_decode:LAYERS       the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64)
-                              cut to LAYERS layers: prompt of 512, then three decoding steps (seeded numpy weights);
-                              prints the device time of a replayed step.  Under `python -m torch.distributed.run
-                              --nproc-per-node N` the decoder is tensor-parallel over N GPUs (one rank per GPU, the
-                              slowest rank's time is printed by rank 0)
+      gpt_decode:LAYERS[:T]   the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64,
+                              prompt 512) cut to LAYERS layers, T new tokens (default 64): prints the gpt_decode record
+                              of the default run.  Under `python -m torch.distributed.run --nproc-per-node N` the decoder
+                              is tensor-parallel over N GPUs (one rank per GPU, the slowest rank's times are printed by rank 0)
     """
-    import numpy as np
     from nn_b200 import native as N
     from nn_b200.device import Device
     name, _, arg = spec.partition(":")
@@ -313,6 +574,22 @@ def run_case(spec: str):
         y = dev.empty(m * n_)
         for _ in range(3):
             N.call("ns_qmatmul_i8", dev.handle, a.ptr, a_s.ptr, w.ptr, w_s.ptr, b.ptr, 0, 0, m, n_, k_, N.EPI_BIAS, N.NS_F32, y.ptr, 0)
+    elif name == "i8_mainloop_peak":
+        kp = int(arg or 16384)
+        a, w = dev.empty(M * kp, N.NS_I8), dev.empty(NN * kp, N.NS_I8)
+        N.call("ns_fill_normal", dev.handle, a.ptr, N.NS_I8, C.c_int64(M * kp), 1, 0.0, 40.0)
+        N.call("ns_fill_normal", dev.handle, w.ptr, N.NS_I8, C.c_int64(NN * kp), 9, 0.0, 40.0)
+        for _ in range(3):
+            N.call("ns_bench_i8_mainloop", dev.handle, a.ptr, w.ptr, M, NN, kp)
+        e0, e1 = dev.event(), dev.event()
+        dev.synchronize()
+        dev.record(e0)
+        for _ in range(200):
+            N.call("ns_bench_i8_mainloop", dev.handle, a.ptr, w.ptr, M, NN, kp)
+        dev.record(e1)
+        us = dev.elapsed_ms(e0, e1) / 200 * 1e3
+        print(json.dumps({"case": spec, "ok": True, "us_per_launch": us, "tops": 2.0 * M * kp * NN / (us * 1e-6) / 1e12, "M": M, "N": NN, "K": kp}))
+        return
     elif name == "attention_decode":
         B, heads, dh, L, ps = 64, 32, 128, int(arg or 1024), 64
         max_pages = (L + ps) // ps
@@ -339,38 +616,12 @@ def run_case(spec: str):
         for _ in range(3):
             N.call("ns_attention_prefill", dev.handle, q.ptr, k.ptr, v.ptr, o.ptr, B, H, S, 128, st, st, st, st, C.c_float(0.0884), 1)
     elif name == "gpt_decode":
-        from nn_b200.gpt import GptConfig, GptW8A8
-        layers, B, prompt_len = int(arg or 2), 64, 512
-        cfg = GptConfig(vocab=32000, dim=2048, heads=16, layers=layers, ff_dim=8192, context=768)
-        rng = np.random.default_rng(4)
-        D, FF, V = cfg.dim, cfg.ff_dim, cfg.vocab
-        nrm = lambda *shape, s=0.02: (rng.standard_normal(shape, dtype=np.float32) * s)
-        w = {"tok": nrm(V, D), "pos": nrm(cfg.context, D), "lnf_g": 1.0 + nrm(D, s=0.05), "lnf_b": nrm(D), "head_w": nrm(D, V), "head_b": nrm(V, s=0.01),
-             "l0.ln1_g": 1.0 + nrm(D, s=0.05), "l0.ln1_b": nrm(D), "l0.ln2_g": 1.0 + nrm(D, s=0.05), "l0.ln2_b": nrm(D),
-             "l0.qkv_w": nrm(D, 3 * D), "l0.qkv_b": nrm(3 * D, s=0.01), "l0.out_w": nrm(D, D), "l0.out_b": nrm(D, s=0.01),
-             "l0.ff1_w": nrm(D, FF), "l0.ff1_b": nrm(FF, s=0.01), "l0.ff2_w": nrm(FF, D), "l0.ff2_b": nrm(D, s=0.01)}
-        from nn_b200 import dist
-        comm, rank, world = dist.init_comm(dev)
-        model = GptW8A8(dev, cfg, w, B, max_prefill=prompt_len, share_layer_weights=True, tp_rank=rank, tp_size=world,
-                        comm=comm)   # every layer its own device copy
-        model.prefill(rng.integers(0, V, (B, prompt_len)).astype(np.int32))
-        for _ in range(3):
-            model.step(False)
-        dev.synchronize()
-        e0, e1 = dev.event(), dev.event()
-        model.step(True)
-        model.step(True)
-        dev.record(e0)
-        for _ in range(20):
-            model.step(True)
-        dev.record(e1)
-        ms = dist.all_reduce_max(dev.elapsed_ms(e0, e1) / 20)
-        dev.synchronize()
-        launches = model.launches_per_step
-        model.close()
+        from nn_b200 import dist as nsdist
+        layers, _, toks = arg.partition(":")
+        rank, world, _ = nsdist.env_rank()
+        rec = run_gpt_decode(dev, rank, world, measured_peaks(), int(layers or 2), int(toks or 64), compare_tp1=False)
         if rank == 0:
-            print(json.dumps({"case": spec, "ok": True, "ms_per_replayed_step": ms, "tokens_per_s": B / ms * 1e3, "layers": layers,
-                              "tensor_parallel": world, "launches_per_step": launches}))
+            print(json.dumps({"case": spec, "ok": True, "gpt_decode": rec}))
         return
     else:
         raise SystemExit(f"unknown case {spec}")
@@ -385,6 +636,10 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-gpt", action="store_true", help="skip the decoder's generation (the int8 product line only)")
+    ap.add_argument("--no-tp1", action="store_true", help="several GPUs: skip the one-GPU run the tokens are compared with")
+    ap.add_argument("--gpt-layers", type=int, default=GPT["layers"])
+    ap.add_argument("--gpt-tokens", type=int, default=GPT["new_tokens"])
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -77,8 +77,12 @@ NS_API int ns_device_stream(ns_device_t dev, uint64_t* stream);
 NS_API int ns_stream_sync(ns_device_t dev);
 /* Reads and clears the device status word: 0 = no kernel gave up a wait. */
 NS_API int ns_device_status(ns_device_t dev, int* status);
-/* Tuning overrides for experiments: tile width (0, 32, 64, 128, 256; 512 = the CTA-pair kernel where a shape allows it,
- * 256 = never the pair kernel) and split-K count (0 = heuristic). */
+/* TEST HOOK, not for hosts: overrides the products' tiling heuristic so that tests and profiler cases can reach
+ * every kernel variant on one shape.  tile_n: 0 = heuristic, 64 / 128 / 256 = that tile width with the single-CTA
+ * kernel, NS_TUNE_NARROW = the narrowest tile, NS_TUNE_PAIR = the CTA-pair kernel wherever a shape allows it.
+ * k_splits: 0 = heuristic, otherwise the split-K count.  A host binding has no reason to import this. */
+#define NS_TUNE_NARROW 32
+#define NS_TUNE_PAIR 512
 NS_API int ns_device_tune(ns_device_t dev, int tile_n, int k_splits);
 
 /* ------------------------------------------------------------------------------------------------
@@ -144,6 +148,12 @@ NS_API int ns_qmatmul_i8(ns_device_t dev, uint64_t aq, uint64_t a_scale, uint64_
  * so calls that overlap on the GPU race.  No raw accumulator output. */
 NS_API int ns_qmatmul_i8_static(ns_device_t dev, uint64_t aq, uint64_t a_scale, uint64_t wq, uint64_t w_scale, uint64_t bias,
                                 uint64_t residual, int residual_dtype, int M, int N, int K, int epilogue, int out_dtype, uint64_t y);
+
+/* BENCH HOOK, not for hosts: the int8 product's main loop alone -- TMA loads and tcgen05 MMAs of the same kernels,
+ * accumulators read from tensor memory and discarded, nothing dequantised and nothing written.  Timing it gives the
+ * int8 tensor-core rate this library's load / MMA pipeline reaches on a shape, the yardstick the full product
+ * (with its epilogue) is compared with.  No counterpart in the reference. */
+NS_API int ns_bench_i8_mainloop(ns_device_t dev, uint64_t aq, uint64_t wq, int M, int N, int K);
 
 /* bf16 product with float accumulation: C[b] = A[b] * op(B[b]); A [m,k] bf16; B [k,n] bf16 (transB = 0)
  * or [n,k] (transB = 1); C [m,n] of out_dtype.  Batch stride = one full matrix, as in the reference.

@@ -259,9 +259,12 @@ __global__ void ns_attention_combine_kernel(const DecodeParams p)
 }
 
 // cache[page(b, pos + i), h, (pos + i) % page_size, :] = src[(b, i), h, :]
+// A negative position, a position beyond the page table or a table entry that names no page of the pool is not written:
+// the store is skipped and code 500 goes to the device status word (the reference throws for positions beyond the
+// capacity, DecodingContext.BeginStep, src/NeuralSharp/Layers/Decoding.cs:96-99).
 __global__ void ns_kv_append_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v, int64_t src_stride, uint16_t* k_pool,
                                     uint16_t* v_pool, const int32_t* __restrict__ page_table, int max_pages, int page_size, int heads, int dh,
-                                    const int32_t* pos_dev, int batch, int steps)
+                                    const int32_t* pos_dev, int batch, int steps, int num_pages, int* status)
 {
     ns_pdl_wait();
     ns_pdl_trigger();
@@ -274,8 +277,9 @@ __global__ void ns_kv_append_kernel(const uint16_t* __restrict__ k, const uint16
         const int64_t tok = e / ((int64_t)vec * heads);
         const int i = (int)(tok % steps), b = (int)(tok / steps);
         const int pos = pos0 + i;
-        if (pos / page_size >= max_pages) continue;
+        if (pos < 0 || pos / page_size >= max_pages) { *reinterpret_cast<volatile int*>(status) = 500; continue; }
         const int page = page_table[(size_t)b * max_pages + pos / page_size];
+        if (page < 0 || page >= num_pages) { *reinterpret_cast<volatile int*>(status) = 500; continue; }
         const size_t dst = (((size_t)page * heads + h) * page_size + pos % page_size) * dh + c * 8;
         const size_t src = (size_t)tok * src_stride + h * dh + c * 8;
         *reinterpret_cast<uint4*>(k_pool + dst) = *reinterpret_cast<const uint4*>(k + src);
@@ -366,7 +370,7 @@ extern "C" int ns_kv_append(ns_device_t h, ns_kv_cache_t ch, uint64_t k, uint64_
     NS_CUDA(ns_launch_plain(ns_kv_append_kernel, dim3((unsigned)blocks), dim3(256), 0, d->stream, reinterpret_cast<const uint16_t*>(k), reinterpret_cast<const uint16_t*>(v), src_stride,
                                                                 c->k_pool, c->v_pool, reinterpret_cast<const int32_t*>(page_table), max_pages,
                                                                 c->page_size, c->heads, c->head_dim, reinterpret_cast<const int32_t*>(pos_dev), batch,
-                                                                steps));
+                                                                steps, c->num_pages, d->status_dev));
     return NS_OK;
 }
 
@@ -374,14 +378,14 @@ extern "C" int ns_kv_append(ns_device_t h, ns_kv_cache_t ch, uint64_t k, uint64_
 struct NsKvCacheView {
     uint16_t* k_pool;
     uint16_t* v_pool;
-    int page_size, heads, head_dim;
+    int page_size, heads, head_dim, num_pages;
 };
 int ns_kv_cache_view(ns_kv_cache_t ch, NsKvCacheView* out)
 {
     NsKvCache* c = reinterpret_cast<NsKvCache*>(ch);
     NS_REQUIRE(c != nullptr && out != nullptr, NS_ERR_ARGUMENT, "cache is null");
     out->k_pool = c->k_pool; out->v_pool = c->v_pool;
-    out->page_size = c->page_size; out->heads = c->heads; out->head_dim = c->head_dim;
+    out->page_size = c->page_size; out->heads = c->heads; out->head_dim = c->head_dim; out->num_pages = c->num_pages;
     return NS_OK;
 }
 

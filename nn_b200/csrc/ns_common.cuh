@@ -37,6 +37,9 @@ int ns_fail(int code, const char* fmt, ...);  // records the message, returns co
 
 // Slots of the device status block kernels write to when a bounded wait gives up.
 enum { NS_STATUS_WORDS = 16 };
+// Device words for grid-wide phases: [0] arrivals, [1] departures of the product kernels' second phase;
+// [NS_SYNC_ROW_TICKETS, +NS_SYNC_MAX_ROWS) one ticket per activation row for the decode attention's row quantisation.
+enum { NS_SYNC_WORDS = 4096, NS_SYNC_ROW_TICKETS = 64, NS_SYNC_MAX_ROWS = 4000 };
 
 struct NsDevice {
     int ordinal = 0;
@@ -49,6 +52,13 @@ struct NsDevice {
     // outside stream capture, reused by every call on the device's stream.
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
+    // A recorded graph keeps the scratch address it was captured with in its kernel arguments and tensor maps.  While
+    // graphs of this device exist, a block that has to grow is retired (kept allocated) instead of freed, so those
+    // graphs keep replaying on valid memory; retired blocks are freed when the last graph is destroyed.
+    int live_graphs = 0;
+    std::vector<void*> retired_scratch;
+    // words for grid-wide phases inside one kernel (arrival counters, per-row tickets); zero between kernels
+    uint32_t* sync_words = nullptr;
     // tuning overrides (0 = heuristic)
     int force_bn = 0;
     int force_splits = 0;

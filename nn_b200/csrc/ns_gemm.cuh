@@ -17,6 +17,8 @@ struct NsGemmParams {
     int residual_dtype;
     int vec_cols;       // 1: w_scale and bias are 16-byte aligned (vector loads in the epilogue)
     int tma_store;      // 1: outputs leave through shared memory and TMA stores; 0: direct stores (odd N)
+    int prefetch_b;     // 1: B is a weight no kernel on the stream writes (Linear objects): its first tiles may be
+                        //    requested before the previous kernel has finished; 0: every load waits for that kernel
     void* out;          // [M, N] or null
     int32_t* raw;       // optional exact accumulators (int8 kind only)
     const float* a_scale;

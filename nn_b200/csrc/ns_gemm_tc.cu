@@ -327,10 +327,11 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         ns_tma_load_2d(b_dst + c * (64 * 128), &tmB, full_bar(s), tn * BN + c * 64, kb * 64);
                 }
             };
-            // B holds weights, which no kernel of the step writes: the first ring-full of B tiles is requested
-            // before waiting for the previous kernel, so its HBM latency overlaps that kernel's tail.
+            // When B holds weights, which no kernel of the step writes (p.prefetch_b, set by the Linear objects only):
+            // the first ring-full of B tiles is requested before waiting for the previous kernel, so its HBM latency
+            // overlaps that kernel's tail.  A caller's own B may have been written by the kernel just before this one.
             int armed = 0;
-            if ((int)blockIdx.x < n_items) {
+            if (p.prefetch_b && (int)blockIdx.x < n_items) {
                 int tm, tn, split;
                 tile_coords(p, blockIdx.x, tm, tn, split);
                 const int kb0 = split * p.kb_per_split;
@@ -851,7 +852,7 @@ void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* b
     const int tiles_m = (M + BM - 1) / BM;
     int bn = 256;
     if (d->force_bn) {
-        bn = d->force_bn == 32 ? 64 : (d->force_bn == 512 ? 256 : d->force_bn);
+        bn = d->force_bn == NS_TUNE_NARROW ? 64 : (d->force_bn == NS_TUNE_PAIR ? 256 : d->force_bn);
     } else if (tiles_m == 1) {
         bn = b_is_kn ? 256 : 128;
         while (bn > 64 && bn / 2 >= N) bn >>= 1;
@@ -896,9 +897,9 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     int bn, splits;
     ns_gemm_choose_tiling(d, M, N, p.k_blocks, &bn, &splits, b_is_kn);
     // Large products with [N, K] weights go to the CTA-pair kernel (256 x 256 tiles over two SMs): whenever 256-wide
-    // tiles without a K split were chosen and there are at least two row tiles.  Tuning override 512 forces it, 256
-    // forces the single-CTA kernel.
-    const bool pair = splits == 1 && M > BM && (d->force_bn == 512 || (d->force_bn == 0 && bn == 256));
+    // tiles without a K split were chosen and there are at least two row tiles.  The test hook NS_TUNE_PAIR forces it,
+    // a tile width of 256 forces the single-CTA kernel.
+    const bool pair = splits == 1 && M > BM && (d->force_bn == NS_TUNE_PAIR || (d->force_bn == 0 && bn == 256));
     p.kb_per_split = (p.k_blocks + splits - 1) / splits;
     p.k_splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
     p.tiles_m = pair ? (M + 255) / 256 : (M + BM - 1) / BM;
@@ -1044,6 +1045,21 @@ extern "C" int ns_qmatmul_i8(ns_device_t h, uint64_t aq, uint64_t a_scale, uint6
     p.w_scale = reinterpret_cast<const float*>(w_scale);
     p.bias = reinterpret_cast<const float*>(bias);
     p.residual = reinterpret_cast<const void*>(residual);
+    return ns_gemm_run(d, NS_KIND_I8, reinterpret_cast<const void*>(aq), reinterpret_cast<const void*>(wq), false, M, N, K, p);
+}
+
+extern "C" int ns_bench_i8_mainloop(ns_device_t h, uint64_t aq, uint64_t wq, int M, int N, int K)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(aq && wq, NS_ERR_ARGUMENT, "ns_bench_i8_mainloop: null operand");
+    NS_REQUIRE(M > 8, NS_ERR_ARGUMENT, "ns_bench_i8_mainloop: meant for the tensor-core kernels (M > 8)");
+    // no output and no raw accumulators: the epilogue warps read tensor memory and hand the accumulator back
+    NsGemmParams p = {};
+    p.epilogue = NS_EPI_NONE;
+    p.out_dtype = NS_F32;
+    p.residual_dtype = NS_F32;
     return ns_gemm_run(d, NS_KIND_I8, reinterpret_cast<const void*>(aq), reinterpret_cast<const void*>(wq), false, M, N, K, p);
 }
 

@@ -150,6 +150,7 @@ extern "C" int ns_linear_forward(ns_device_t h, ns_linear_t lh, uint64_t x, uint
     p.a_scale = reinterpret_cast<const float*>(x_scale);
     p.w_scale = L->w_scale;
     p.bias = epilogue == NS_EPI_NONE ? nullptr : L->bias;
+    p.prefetch_b = 1;   // the layer's weights were written before a synchronisation (ns_linear_create)
     p.residual = reinterpret_cast<const void*>(residual);
     return ns_gemm_run(d, L->mode == NS_I8 ? NS_KIND_I8 : NS_KIND_BF16, reinterpret_cast<const void*>(x), L->w, false, M, L->N_loc, L->K_loc, p);
 }
@@ -173,6 +174,7 @@ int ns_linear_forward_on(NsDevice* d, NsLinear* L, const void* x, const float* x
     p.a_scale = x_scale;
     p.w_scale = L->w_scale;
     p.bias = epilogue == NS_EPI_NONE ? nullptr : L->bias;
+    p.prefetch_b = 1;   // the layer's weights were written before a synchronisation (ns_linear_create)
     return ns_gemm_run(d, L->mode == NS_I8 ? NS_KIND_I8 : NS_KIND_BF16, x, L->w, false, M, L->N_loc, L->K_loc, p);
 }
 
@@ -192,6 +194,7 @@ extern "C" int ns_linear_forward_partial(ns_device_t h, ns_linear_t lh, uint64_t
     p.epilogue = NS_EPI_NONE;
     p.out_dtype = NS_F32;
     p.residual_dtype = NS_F32;
+    p.prefetch_b = 1;
     void* ptr = nullptr;
     int s = 0;
     rc = ns_gemm_run(d, NS_KIND_I8, reinterpret_cast<const void*>(x), L->w, false, M, L->N_loc, L->K_loc, p, nullptr, 0, &ptr, &s);

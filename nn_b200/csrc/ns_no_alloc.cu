@@ -58,11 +58,18 @@ extern "C" int ns_qmatmul_i8_static(ns_device_t h, uint64_t aq, uint64_t a_scale
     NS_REQUIRE(epilogue == NS_EPI_NONE || bias != 0, NS_ERR_ARGUMENT, "ns_qmatmul_i8_static: epilogue %d needs a bias vector", epilogue);
     NS_REQUIRE(epilogue != NS_EPI_BIAS_RESIDUAL || residual != 0, NS_ERR_ARGUMENT, "ns_qmatmul_i8_static: NS_EPI_BIAS_RESIDUAL needs a residual");
     NS_REQUIRE(out_dtype == NS_F32 || out_dtype == NS_BF16, NS_ERR_ARGUMENT, "ns_qmatmul_i8_static: output must be NS_F32 or NS_BF16");
+    NS_REQUIRE(residual_dtype == NS_F32 || residual_dtype == NS_BF16, NS_ERR_ARGUMENT, "ns_qmatmul_i8_static: residual dtype must be NS_F32 or NS_BF16");
     NS_REQUIRE(M > 0 && N > 0 && K > 0, NS_ERR_ARGUMENT, "ns_qmatmul_i8_static: empty dimension");
     // size check first, so that an oversized request fails before anything is queued
+    // (the split count the launcher ends up with: the requested count shrinks when the k-blocks do not divide evenly;
+    // one to eight rows take the row-streaming kernel, which has no partial sums)
     int tile_n = 0, splits = 1;
-    ns_gemm_choose_tiling(d, M, N, (K + 127) / 128, &tile_n, &splits);
-    const size_t need = splits > 1 ? (size_t)splits * M * N * 4 : 0;
+    const int k_blocks = (K + 127) / 128;
+    ns_gemm_choose_tiling(d, M, N, k_blocks, &tile_n, &splits);
+    const int kb_per_split = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + kb_per_split - 1) / kb_per_split;
+    const bool streams_rows = d->force_bn == 0 && d->force_splits == 0 && ns_gemv_i8_fits(M, K) && ((aq | wq) & 15) == 0;
+    const size_t need = (splits > 1 && !streams_rows) ? (size_t)splits * M * N * 4 : 0;
     NS_REQUIRE(need <= NS_STATIC_SCRATCH_BYTES, NS_ERR_MEMORY,
                "ns_qmatmul_i8_static: M=%d N=%d K=%d splits K %d ways and needs %zu bytes of partial sums; the fixed scratch array holds %u",
                M, N, K, splits, need, (unsigned)NS_STATIC_SCRATCH_BYTES);
@@ -72,7 +79,7 @@ extern "C" int ns_qmatmul_i8_static(ns_device_t h, uint64_t aq, uint64_t a_scale
     NsGemmParams p = {};
     p.epilogue = epilogue;
     p.out_dtype = out_dtype;
-    p.residual_dtype = residual_dtype == NS_BF16 ? NS_BF16 : NS_F32;
+    p.residual_dtype = residual_dtype;
     p.out = reinterpret_cast<void*>(y);
     p.a_scale = reinterpret_cast<const float*>(a_scale);
     p.w_scale = reinterpret_cast<const float*>(w_scale);

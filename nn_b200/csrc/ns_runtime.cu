@@ -97,6 +97,15 @@ static int open_device(int ordinal, bool own_stream, cudaStream_t stream, ns_dev
         return ns_fail(NS_ERR_CUDA, "status block allocation failed: %s (%d)", cudaGetErrorName(e), (int)e);
     }
     memset(d->status_host, 0, NS_STATUS_WORDS * sizeof(int));
+    e = cudaMalloc(reinterpret_cast<void**>(&d->sync_words), NS_SYNC_WORDS * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(d->sync_words, 0, NS_SYNC_WORDS * sizeof(uint32_t));
+    if (e != cudaSuccess) {
+        if (d->sync_words) cudaFree(d->sync_words);
+        cudaFreeHost(d->status_host);
+        if (own_stream) cudaStreamDestroy(d->stream);
+        delete d;
+        return ns_fail(NS_ERR_MEMORY, "synchronisation words: %s (%d)", cudaGetErrorName(e), (int)e);
+    }
     *out = reinterpret_cast<ns_device_t>(d);
     return NS_OK;
 }
@@ -117,6 +126,8 @@ extern "C" int ns_device_close(ns_device_t h)
     cudaStreamSynchronize(d->stream);
     if (d->host_pipe && d->host_pipe_free) d->host_pipe_free(d->host_pipe);
     if (d->scratch) cudaFree(d->scratch);
+    for (void* p : d->retired_scratch) cudaFree(p);
+    if (d->sync_words) cudaFree(d->sync_words);
     if (d->status_host) cudaFreeHost(d->status_host);
     if (d->owns_stream && d->stream) cudaStreamDestroy(d->stream);
     delete d;
@@ -174,8 +185,8 @@ extern "C" int ns_device_tune(ns_device_t h, int tile_n, int k_splits)
 {
     NsDevice* d = ns_dev(h);
     NS_REQUIRE(d != nullptr, NS_ERR_ARGUMENT, "ns_device_tune: device is null");
-    NS_REQUIRE(tile_n == 0 || tile_n == 32 || tile_n == 64 || tile_n == 128 || tile_n == 256 || tile_n == 512, NS_ERR_ARGUMENT,
-               "ns_device_tune: tile_n must be 0, 32, 64, 128, 256 or 512");
+    NS_REQUIRE(tile_n == 0 || tile_n == NS_TUNE_NARROW || tile_n == 64 || tile_n == 128 || tile_n == 256 || tile_n == NS_TUNE_PAIR, NS_ERR_ARGUMENT,
+               "ns_device_tune: tile_n must be 0, 64, 128, 256, NS_TUNE_NARROW or NS_TUNE_PAIR");
     NS_REQUIRE(k_splits >= 0 && k_splits <= 64, NS_ERR_ARGUMENT, "ns_device_tune: k_splits must be in [0, 64]");
     d->force_bn = tile_n;
     d->force_splits = k_splits;
@@ -188,7 +199,11 @@ int ns_scratch_reserve(NsDevice* d, size_t bytes, void** out)
         NS_REQUIRE(!d->capturing, NS_ERR_STATE,
                    "scratch memory must grow to %zu bytes but the stream is being captured; run the step once before capturing", bytes);
         NS_CUDA(cudaStreamSynchronize(d->stream));
-        if (d->scratch) NS_CUDA(cudaFree(d->scratch));
+        if (d->scratch) {
+            // graphs recorded earlier still name the old block: keep it until the last of them is destroyed
+            if (d->live_graphs > 0) d->retired_scratch.push_back(d->scratch);
+            else NS_CUDA(cudaFree(d->scratch));
+        }
         d->scratch = nullptr;
         d->scratch_bytes = 0;
         size_t want = bytes + (bytes >> 2);
@@ -330,6 +345,7 @@ struct NsGraph {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int ordinal = 0;
+    NsDevice* dev = nullptr;
 };
 
 extern "C" int ns_capture_begin(ns_device_t h)
@@ -353,6 +369,7 @@ extern "C" int ns_capture_end(ns_device_t h, ns_graph_t* out)
     d->capturing = 0;
     NsGraph* g = new NsGraph();
     g->ordinal = d->ordinal;
+    g->dev = d;
     cudaError_t e = cudaStreamEndCapture(d->stream, &g->graph);
     if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
     if (e != cudaSuccess) {
@@ -360,6 +377,10 @@ extern "C" int ns_capture_end(ns_device_t h, ns_graph_t* out)
         delete g;
         cudaGetLastError();
         return ns_fail(NS_ERR_CUDA, "graph capture failed: %s (%d)", cudaGetErrorName(e), (int)e);
+    }
+    {
+        std::lock_guard<std::mutex> guard(d->lock);
+        d->live_graphs++;
     }
     *out = reinterpret_cast<ns_graph_t>(g);
     return NS_OK;
@@ -397,6 +418,19 @@ extern "C" int ns_graph_destroy(ns_graph_t gh)
     cudaSetDevice(g->ordinal);
     if (g->exec) cudaGraphExecDestroy(g->exec);
     if (g->graph) cudaGraphDestroy(g->graph);
+    // Must be called before ns_device_close of the graph's device.  With the last graph gone nothing names a retired
+    // scratch block any more (a replay still in flight is waited for first).
+    if (NsDevice* d = g->dev) {
+        std::lock_guard<std::mutex> guard(d->lock);
+        if (--d->live_graphs <= 0) {
+            d->live_graphs = 0;
+            if (!d->retired_scratch.empty()) {
+                cudaStreamSynchronize(d->stream);
+                for (void* p : d->retired_scratch) cudaFree(p);
+                d->retired_scratch.clear();
+            }
+        }
+    }
     delete g;
     return NS_OK;
 }

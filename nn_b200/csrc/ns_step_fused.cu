@@ -21,7 +21,7 @@
 struct NsKvCacheView {
     uint16_t* k_pool;
     uint16_t* v_pool;
-    int page_size, heads, head_dim;
+    int page_size, heads, head_dim, num_pages;
 };
 int ns_kv_cache_view(ns_kv_cache_t cache, NsKvCacheView* out);   // ns_attention_decode.cu
 
@@ -200,8 +200,9 @@ struct FinishKvParams {
     uint16_t* k_pool;
     uint16_t* v_pool;
     const int32_t* page_table;
-    int max_pages, page_size, heads, dh;
+    int max_pages, page_size, heads, dh, num_pages;
     const int32_t* pos_dev;
+    int* status;
 };
 
 // One thread per 8 consecutive columns of a row.
@@ -242,8 +243,10 @@ __global__ void ns_finish_kv_append_kernel(const FinishKvParams p)
         const int h = in_third / p.dh, c = in_third % p.dh;
         const int i = (int)(row % p.steps), b = (int)(row / p.steps);
         const int pos = pos0 + i;
-        if (pos / p.page_size >= p.max_pages) continue;
+        // an append outside the cache is skipped and reported (code 500), as in ns_kv_append
+        if (pos < 0 || pos / p.page_size >= p.max_pages) { *reinterpret_cast<volatile int*>(p.status) = 500; continue; }
         const int page = p.page_table[(size_t)b * p.max_pages + pos / p.page_size];
+        if (page < 0 || page >= p.num_pages) { *reinterpret_cast<volatile int*>(p.status) = 500; continue; }
         const size_t dst = (((size_t)page * p.heads + h) * p.page_size + pos % p.page_size) * p.dh + c;
         *reinterpret_cast<uint4*>((third == 1 ? p.k_pool : p.v_pool) + dst) = out;
     }
@@ -331,8 +334,9 @@ extern "C" int ns_finish_kv_append(ns_device_t h, uint64_t partial, int splits, 
     p.qkv = reinterpret_cast<uint16_t*>(qkv);
     p.k_pool = c.k_pool; p.v_pool = c.v_pool;
     p.page_table = reinterpret_cast<const int32_t*>(page_table);
-    p.max_pages = max_pages; p.page_size = c.page_size; p.heads = c.heads; p.dh = c.head_dim;
+    p.max_pages = max_pages; p.page_size = c.page_size; p.heads = c.heads; p.dh = c.head_dim; p.num_pages = c.num_pages;
     p.pos_dev = reinterpret_cast<const int32_t*>(pos_dev);
+    p.status = d->status_dev;
     int64_t blocks = (n + 255) / 256;
     if (blocks > (int64_t)d->sm_count * 16) blocks = (int64_t)d->sm_count * 16;
     NS_CUDA(ns_launch_plain(ns_finish_kv_append_kernel, dim3((unsigned)blocks), dim3(256), 0, d->stream, p));

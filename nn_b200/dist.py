@@ -89,3 +89,60 @@ def all_reduce_max(value: float) -> float:
     t = torch.tensor([value], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+class PeerWatch:
+    """Host-side failure detection for a multi-rank decoder, checked BETWEEN steps (no kernel or collective in flight).
+
+    Every rank publishes the number of the step it is about to queue in a key-value store all ranks reach (the store of
+    the torch.distributed rendezvous by default); before queuing step s a rank waits, for at most `timeout_s`, until
+    every peer has published s.  A peer that left (crashed, or returned from its loop) never does: the waiting rank then
+    tears its communicator down with `comm_abort` (ns_comm_abort: it must not wait for the missing peer) and raises
+    NsError with NS_ERR_COMM, before anything that would wait for that peer on the GPU is launched.  `comm_error`, when
+    given, is polled as well (ns_comm_async_error's result: non-zero = the transport itself reported a failure).
+    The reference is single-process; the error convention is its CudaDriver.Check (Backends/Cuda/CudaDriver.cs:63-77).
+    """
+
+    NS_ERR_COMM = 5
+
+    def __init__(self, rank: int, world: int, timeout_s: float = 30.0, store=None, comm_error=None, comm_abort=None, prefix: str = "ns_watch"):
+        if store is None:
+            import torch.distributed as dist
+            store = dist.distributed_c10d._get_default_store()
+        self.store, self.rank, self.world, self.timeout_s = store, rank, world, timeout_s
+        self.comm_error, self.comm_abort, self.prefix = comm_error, comm_abort, prefix
+        self.aborted = False
+
+    def _key(self, rank: int) -> str:
+        return f"{self.prefix}/{rank}"
+
+    def _fail(self, text: str):
+        if self.comm_abort is not None and not self.aborted:
+            self.comm_abort()
+        self.aborted = True
+        raise N.NsError("PeerWatch.check", self.NS_ERR_COMM, text)
+
+    def check(self, step: int) -> None:
+        """Call before queuing step `step` (0, 1, 2, ... in order)."""
+        import time
+        self.store.set(self._key(self.rank), str(step))
+        deadline = time.monotonic() + self.timeout_s
+        for peer in range(self.world):
+            if peer == self.rank:
+                continue
+            while True:
+                if self.comm_error is not None:
+                    code = self.comm_error()
+                    if code:
+                        self._fail(f"the transport reports error {code} before step {step}")
+                seen = -1
+                try:
+                    if self.store.check([self._key(peer)]):
+                        seen = int(self.store.get(self._key(peer)))
+                except Exception as e:          # the store itself went away with the rank that served it
+                    self._fail(f"rendezvous store unreachable before step {step}: {e}")
+                if seen >= step:
+                    break
+                if time.monotonic() > deadline:
+                    self._fail(f"rank {peer} did not reach step {step} within {self.timeout_s:.1f} s (last seen at step {seen})")
+                time.sleep(0.005)

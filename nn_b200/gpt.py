@@ -85,12 +85,12 @@ class GptW8A8:
     """weights: dict of float32 arrays in the reference's layouts --
     tok [V, D], pos [context, D], lnf_g, lnf_b [D], head_w [D, V], head_b [V], and per layer i:
     ln1_g, ln1_b, qkv_w [D, 3D], qkv_b, out_w [D, D], out_b, ln2_g, ln2_b, ff1_w [D, FF], ff1_b, ff2_w [FF, D], ff2_b
-    under keys f"l{i}.<name>" (Linear.Weight is [in, out], Layers/Linear.cs:25-27).
-    share_layer_weights: build every layer from layer 0's arrays (distinct device copies) -- synthetic benchmarks only.
+    under keys f"l{i}.<name>" (Linear.Weight is [in, out], Layers/Linear.cs:25-27).  Any mapping works: every tensor
+    is looked up once, layer by layer, so a caller may produce them on demand.
     """
 
     def __init__(self, dev: Device, cfg: GptConfig, weights: dict, batch: int, max_prefill: int, tp_rank: int = 0, tp_size: int = 1,
-                 comm=None, page_size: int = 64, share_layer_weights: bool = False, peer_exchange: bool = True):
+                 comm=None, page_size: int = 64, peer_exchange: bool = True):
         assert cfg.dim % cfg.heads == 0 and cfg.heads % tp_size == 0 and cfg.ff_dim % tp_size == 0 and cfg.vocab % tp_size == 0
         assert tp_size == 1 or comm is not None
         self.dev, self.cfg, self.batch, self.rank, self.tp, self.comm = dev, cfg, batch, tp_rank, tp_size, comm
@@ -104,7 +104,7 @@ class GptW8A8:
         self.head = _Linear(dev, weights["head_w"], weights["head_b"], col, 1, tp_rank, tp_size)
         self.layers = []
         for i in range(cfg.layers):
-            w = (lambda name, i=i: weights[f"l{0 if share_layer_weights else i}.{name}"])
+            w = (lambda name, i=i: weights[f"l{i}.{name}"])
             self.layers.append({
                 "ln1": (dev.from_numpy(w("ln1_g").astype(np.float32)), dev.from_numpy(w("ln1_b").astype(np.float32))),
                 "ln2": (dev.from_numpy(w("ln2_g").astype(np.float32)), dev.from_numpy(w("ln2_b").astype(np.float32))),
@@ -133,6 +133,7 @@ class GptW8A8:
         # few-row passes on several GPUs exchange their partial rows through peer memory (one fused kernel per half-layer)
         self.peer = None
         self.peer_slots = None
+        self._peer_all = self._peer_solo = None
         if tp_size > 1 and peer_exchange and D % 256 == 0 and D <= 8192:
             from . import dist
             self.peer = dist.make_peer_group(dev, tp_rank, tp_size, FUSED_MAX_ROWS * D * 4)
@@ -141,6 +142,7 @@ class GptW8A8:
                 ptr = C.c_uint64()
                 N.call("ns_peer_group_slot", self.peer, slot, C.byref(ptr))
                 self.peer_slots.append(ptr.value)
+            self._peer_all = (self.peer, self.peer_slots)
         self.last = dev.empty(batch * D, N.NS_BF16)
         self.logits = dev.empty(batch * self.v_loc, N.NS_F32)
         self.ids = dev.zeros(self.max_rows, N.NS_I32)          # prompt ids during prefill; ids[0:batch] = current tokens while decoding
@@ -377,15 +379,51 @@ class GptW8A8:
             self.dev.graph_launch(self.graph)
         self.length += 1
 
+    def set_local_exchange(self, local: bool) -> None:
+        """Measurement aid for several GPUs: with local=True the exchange kernel of the few-row pass runs in its
+        single-rank form (this rank's own partial rows only: no flag traffic, no peer loads), so the step's time without
+        the cross-GPU exchange can be measured.  The results are then NOT the model's.  The recorded step is dropped."""
+        if self._peer_all is None:
+            return
+        if local and self._peer_solo is None:
+            solo = C.c_void_p()
+            N.call("ns_peer_group_create", self.dev.handle, 0, 1, C.c_uint64(FUSED_MAX_ROWS * self.cfg.dim * 4), C.byref(solo))
+            slots = []
+            for slot in range(2):
+                ptr = C.c_uint64()
+                N.call("ns_peer_group_slot", solo, slot, C.byref(ptr))
+                slots.append(ptr.value)
+            self._peer_solo = (solo, slots)
+        self.peer, self.peer_slots = self._peer_solo if local else self._peer_all
+        if self.graph is not None:
+            self.dev.synchronize()
+            self.dev.graph_destroy(self.graph)
+            self.graph = None
+
     def read_ids(self) -> np.ndarray:
         return self.ids.download(count=self.batch).copy()
 
     def read_logits(self) -> np.ndarray:
         return self.logits.download((self.batch, self.v_loc))
 
-    def generate(self, prompt: np.ndarray, n_new: int, use_graph: bool = True) -> tuple[np.ndarray, int]:
-        """Greedy decoding of n_new tokens per sequence; returns (tokens [batch, n_new], context resets)."""
+    def generate(self, prompt: np.ndarray, n_new: int, use_graph: bool = True, marks: dict | None = None,
+                 mark_every: int = 32) -> tuple[np.ndarray, int]:
+        """Greedy decoding of n_new tokens per sequence; returns (tokens [batch, n_new], context resets).
+        marks: when a dict is given, device events are recorded into it on the device's stream -- "start" (before the
+        prompt is read), "prefill_end" (the first token is on the device), "steps" = [(tokens produced so far, event), ...]
+        every mark_every decoding steps and after the last one -- for timing a generation from outside."""
         cfg, B = self.cfg, self.batch
+
+        def mark(name=None, count=None):
+            if marks is None:
+                return
+            e = self.dev.event()
+            self.dev.record(e)
+            if name is not None:
+                marks[name] = e
+            else:
+                marks.setdefault("steps", []).append((count, e))
+
         history = [list(map(int, row)) for row in np.asarray(prompt)]
         hist_dev = self.dev.empty(B * max(n_new, 1), N.NS_I32)
         pending = 0            # tokens sampled on the device and not yet fetched
@@ -409,8 +447,10 @@ class GptW8A8:
         def window(keep):
             return np.array([h[-keep:] for h in history], dtype=np.int32)
 
+        mark("start")
         self.prefill(window(min(len(history[0]), cfg.context - 1)))
         keep_token()
+        mark("prefill_end")
         produced = 1
         while produced < n_new:
             if self.length >= cfg.context:
@@ -423,6 +463,8 @@ class GptW8A8:
             self.step(use_graph)
             keep_token()
             produced += 1
+            if (produced - 1) % mark_every == 0 or produced == n_new:
+                mark(count=produced)
         flush()
         self.dev.synchronize()
         return np.array(out, dtype=np.int32)[:, :n_new], resets
@@ -431,13 +473,15 @@ class GptW8A8:
         if self.graph is not None:
             self.dev.graph_destroy(self.graph)
             self.graph = None
-        if self.peer is not None:
+        if self._peer_all is not None:
             # no rank may unmap its block while a peer's kernel can still read it
             from . import dist
             self.dev.synchronize()
             dist.barrier()
-            N.call("ns_peer_group_destroy", self.peer)
-            self.peer = None
+            N.call("ns_peer_group_destroy", self._peer_all[0])
+            if self._peer_solo is not None:
+                N.call("ns_peer_group_destroy", self._peer_solo[0])
+            self.peer = self._peer_all = self._peer_solo = None
         for c in self.caches:
             N.call("ns_kv_cache_destroy", c)
         self.caches = []

@@ -53,6 +53,7 @@ SIGNATURES = {
     "ns_quantize_rows_i8": [vp, u64, i32, i64, i32, u64, u64],
     "ns_qmatmul_i8": [vp, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, u64, u64],
     "ns_qmatmul_i8_static": [vp, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, u64],
+    "ns_bench_i8_mainloop": [vp, u64, u64, i32, i32, i32],
     "ns_matmul_bf16": [vp, u64, u64, u64, i32, i32, i32, i32, i32, u64, u64, i32, i32, i32],
     "ns_layernorm": [vp, u64, i32, u64, u64, i64, i32, f32, i32, u64, u64],
     "ns_embed_pos": [vp, u64, u64, u64, i32, u64, i32, i32, i32, i32, i32, i32, u64],

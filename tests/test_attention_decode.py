@@ -123,3 +123,47 @@ def test_baseline_decode_shape(dev, orc):
         exp = orc.attention_slice(orc.widen_bf16(q[b, :, h]), kf, vf, L - 1, scale)
         assert orc.close(orc.bf16_round_trip(exp), got[b, :, h], TOL), (b, h, orc.max_err(exp, got[b, :, h]))
     cache.close()
+
+
+def test_append_outside_the_cache_is_skipped_and_reported(dev, orc):
+    """A page-table entry that names no page of the pool, or a position beyond the table: nothing is written, the next
+    synchronisation reports NS_ERR_KERNEL (status 500), and the device stays usable.  (The reference throws for a
+    position beyond the capacity: DecodingContext.BeginStep, Layers/Decoding.cs:96-99.)"""
+    import ctypes as C
+    B, heads, dh, page_size, max_pages = 2, 2, 64, 16, 4
+    cache = C.c_void_p()
+    N.call("ns_kv_cache_create", dev.handle, B * max_pages, page_size, heads, dh, C.byref(cache))
+    kp, vp, nbytes = C.c_uint64(), C.c_uint64(), C.c_uint64()
+    N.call("ns_kv_cache_pools", cache, C.byref(kp), C.byref(vp), C.byref(nbytes))
+    k = dev.from_numpy(orc.round_bf16(orc.normal((B, heads * dh), 61)))
+    v = dev.from_numpy(orc.round_bf16(orc.normal((B, heads * dh), 62)))
+
+    def pool_bytes():
+        host = np.empty(nbytes.value // 2, np.uint16)
+        N.call("ns_d2h", dev.handle, host.ctypes.data_as(C.c_void_p), kp, nbytes)
+        return host
+
+    for table_host, pos0 in ((np.array([0, 1, 2, 3, 4, 5, 999, 7], np.int32), 35),      # sequence 1, page 2 -> entry 999
+                             (np.arange(B * max_pages, dtype=np.int32), page_size * max_pages),   # position past the table
+                             (np.arange(B * max_pages, dtype=np.int32), -3)):
+        dev.synchronize()
+        table = dev.from_numpy(table_host)
+        pos = dev.from_numpy(np.array([pos0], np.int32))
+        before = pool_bytes()
+        N.call("ns_kv_append", dev.handle, cache, k.ptr, v.ptr, C.c_int64(heads * dh), table.ptr, max_pages, pos.ptr, B, 1)
+        with pytest.raises(N.NsError) as err:
+            dev.synchronize()
+        assert err.value.code == 4 and "status 500" in str(err.value)
+        after = pool_bytes()
+        if pos0 == 35:
+            # sequence 0 (a valid entry) was appended, sequence 1 was skipped
+            changed = np.nonzero(before != after)[0]
+            assert changed.size > 0 and changed.max() < 3 * heads * page_size * dh
+        else:
+            assert np.array_equal(before, after)
+    # still usable
+    table = dev.from_numpy(np.arange(B * max_pages, dtype=np.int32))
+    pos = dev.from_numpy(np.array([5], np.int32))
+    N.call("ns_kv_append", dev.handle, cache, k.ptr, v.ptr, C.c_int64(heads * dh), table.ptr, max_pages, pos.ptr, B, 1)
+    dev.synchronize()
+    N.call("ns_kv_cache_destroy", cache)

@@ -80,3 +80,37 @@ def test_cta_pair_kernel(dev, orc, m, n, k, transB):
         dev.tune(0, 0)
     exp = orc.matmul_bf16(a, b, b_is_nk=transB)
     assert orc.close(exp, c, 1e-4), f"max err {orc.max_err(exp, c)}"
+
+
+def test_equals_the_reference_float_product_on_widened_operands(dev, orc):
+    """The reference's float product (CpuMatMul.cs:102-148, one FMA chain over k per output) on the bf16 operands widened
+    to float is the same sum in another order: float output within K * 2^-23 of the terms' magnitudes."""
+    m, n, k = 96, 384, 2048
+    a = orc.round_bf16(orc.normal((m, k), 41))
+    b = orc.round_bf16(orc.normal((k, n), 42))
+    c = _run(dev, a, b, m, n, k, False, out_dtype=N.NS_F32)[0]
+    af, bf = orc.widen_bf16(a), orc.widen_bf16(b)
+    ref = orc.matmul_f32(af, bf, 1, m, n, k)
+    bound = k * 2.0 ** -23 * (np.abs(af).astype(np.float64) @ np.abs(bf).astype(np.float64))
+    assert np.all(np.abs(ref.astype(np.float64) - c.astype(np.float64)) <= bound)
+
+
+def test_chained_products_without_synchronisation(dev, orc):
+    """C1 = A . B then C2 = D . C1 queued back to back: the second product's B operand is what the first one writes.  A
+    product may begin while the kernel before it is still running (programmatic dependent launch), so the raw entry
+    point must not fetch B before that kernel has finished; the early fetch is reserved for Linear objects."""
+    m, k, n, m2 = 256, 512, 384, 192
+    a = orc.round_bf16(orc.normal((m, k), 51))
+    b = orc.round_bf16(orc.normal((k, n), 52, 0.05))
+    dmat = orc.round_bf16(orc.normal((m2, m), 53, 0.05))
+    d_a, d_b, d_d = dev.from_numpy(a), dev.from_numpy(b), dev.from_numpy(dmat)
+    for rep in range(3):
+        c1 = dev.zeros(m * n, N.NS_BF16)
+        c2 = dev.empty(m2 * n, N.NS_F32)
+        dev.synchronize()
+        N.call("ns_matmul_bf16", dev.handle, d_a.ptr, d_b.ptr, c1.ptr, 1, m, n, k, 0, 0, 0, 0, N.EPI_NONE, N.NS_BF16)
+        N.call("ns_matmul_bf16", dev.handle, d_d.ptr, c1.ptr, c2.ptr, 1, m2, n, m, 0, 0, 0, 0, N.EPI_NONE, N.NS_F32)
+        dev.synchronize()
+        c1_host = c1.download((m, n))
+        exp = orc.matmul_bf16(dmat, c1_host, b_is_nk=False)
+        assert orc.close(exp, c2.download((m2, n)), 1e-4), f"repetition {rep}: the second product read B before it was written"

@@ -188,3 +188,23 @@ def test_row_streaming_kernel_bit_exact(dev, orc, M, Nn, K):
     assert np.array_equal(raw_tc, acc)
     assert np.array_equal(y_tc.view(np.uint32), exp.view(np.uint32))
     assert np.array_equal(yg_tc.view(np.uint32), yg.view(np.uint32)), "GELU epilogue differs between the two kernels"
+
+
+@pytest.mark.parametrize("M", [16, 128])
+def test_equals_the_reference_float_linear_on_dequantised_operands(dev, orc, M):
+    """The float32-only reference computes this Linear as x . W + b with its float product on whatever the operands
+    are (Layers/Linear.cs:43-47 -> CpuMatMul.cs:102-148).  Given the de-quantised operands (aq * a_scale, wq * w_scale)
+    that product must agree with the int8 path up to float rounding: the int8 path is exact up to its three final
+    roundings, the float FMA chain over k carries at most K * 2^-24 of the sum of the terms' magnitudes."""
+    K = Nn = 4096
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=1)
+    y, _ = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS, want_raw=False)
+    a_deq = (aq.astype(np.float32) * a_s[:, None]).astype(np.float32)          # exact in float: |q| <= 127
+    w_deq_kn = np.ascontiguousarray((wq.astype(np.float32) * w_s[:, None]).T)    # Linear.Weight layout [K, N]
+    ref = orc.matmul_f32(a_deq, w_deq_kn, 1, M, Nn, K) + bias[None, :]
+    magnitude = np.abs(a_deq).astype(np.float64) @ np.abs(w_deq_kn).astype(np.float64) + np.abs(bias)[None, :]
+    bound = K * 2.0 ** -23 * magnitude
+    err = np.abs(ref.astype(np.float64) - y.astype(np.float64))
+    assert np.all(err <= bound), f"largest excess {float((err - bound).max()):.3e}"
+    # and the bound is not vacuous: it is far below the spread of the outputs
+    assert float(bound.max()) < 1e-2 * float(np.abs(ref).mean())

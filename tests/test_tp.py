@@ -30,6 +30,12 @@ def test_two_gloo_ranks_on_cpu():
     assert res.stdout.count("cpu ok") == 2
 
 
+def test_a_rank_that_leaves_between_steps_is_noticed_on_the_host():
+    res = _launch("watch", 2)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "saw rank 1 leave" in res.stdout and "left after three steps" in res.stdout
+
+
 @pytest.mark.gpu
 def test_decoder_on_two_gpus():
     from nn_b200.device import Device

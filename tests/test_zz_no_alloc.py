@@ -35,6 +35,11 @@ def test_matches_the_allocating_entry_point_twice_in_a_row(dev, orc):
     M, Nn, K = 64, 2048, 8192
     ref, new = _both(dev, _operands(dev, orc, M, Nn, K, 501), M, Nn, K, N.EPI_BIAS, N.NS_F32)
     assert np.array_equal(ref.view(np.uint32), new.view(np.uint32))        # tolerance 0: same kernels, same order
+    # and directly against the oracle (same operands, regenerated on the host)
+    aq, a_s = orc.quantize_rows_i8(orc.normal((M, K), 501))
+    wq, w_s = orc.quantize_rows_i8(orc.normal((Nn, K), 502, 0.02))
+    exp = orc.dequant_epilogue(orc.qmatmul_i8_acc(aq, wq), a_s, w_s, orc.normal((Nn,), 503, 0.01))
+    assert np.array_equal(new.reshape(M, Nn).view(np.uint32), exp.view(np.uint32))
     M2, N2, K2 = 48, 1024, 4096
     ref, new = _both(dev, _operands(dev, orc, M2, N2, K2, 601), M2, N2, K2, N.EPI_BIAS_GELU, N.NS_BF16)
     assert np.array_equal(ref, new)
@@ -56,3 +61,59 @@ def test_rejects_shapes_beyond_the_fixed_array(dev, orc):
     finally:
         dev.tune(0, 0)
     dev.synchronize()
+
+
+@pytest.mark.parametrize("M,Nn,K", [(4, 1024, 2048), (512, 1024, 1024)])
+def test_shapes_that_need_no_partial_sums(dev, orc, M, Nn, K):
+    """Four rows take the row-streaming kernel, 512 rows are not split along K: neither touches the fixed array, both must
+    equal the regular entry point bit for bit."""
+    ref, new = _both(dev, _operands(dev, orc, M, Nn, K, 901), M, Nn, K, N.EPI_BIAS, N.NS_F32)
+    assert np.array_equal(ref.view(np.uint32), new.view(np.uint32))
+
+
+def test_allocates_nothing_and_can_be_recorded(dev, orc):
+    """The reason the entry point exists: free device memory is the same before and after calls with shapes it has not
+    seen (the regular entry point would grow its scratch block), and after one warm call a call can be recorded into
+    a graph and replayed."""
+    import ctypes as C
+    M, Nn, K = 32, 4096, 4096
+    ops = _operands(dev, orc, 48, Nn, K, 951)      # 48 rows of activations; the calls below use the first m of them
+    y = dev.empty(48 * Nn)
+    y_ref = dev.empty(M * Nn)
+    # one warm call with the kernels the shapes below use (the CUDA runtime loads a kernel's code on its first launch)
+    N.call("ns_qmatmul_i8_static", dev.handle, ops[0].ptr, ops[1].ptr, ops[2].ptr, ops[3].ptr, ops[4].ptr, 0, 0, 16, Nn, K, N.EPI_BIAS, N.NS_F32, y.ptr)
+    dev.synchronize()
+
+    def free_bytes():
+        fr = C.c_uint64()
+        N.call("ns_device_info", dev.handle, None, None, None, C.byref(fr))
+        return fr.value
+
+    before = free_bytes()
+    for m in (24, 32, 48):       # shapes not seen before, all split along K
+        N.call("ns_qmatmul_i8_static", dev.handle, ops[0].ptr, ops[1].ptr, ops[2].ptr, ops[3].ptr, ops[4].ptr, 0, 0, m, Nn, K, N.EPI_BIAS, N.NS_F32, y.ptr)
+    dev.synchronize()
+    assert free_bytes() == before
+    dev.capture_begin()
+    try:
+        N.call("ns_qmatmul_i8_static", dev.handle, ops[0].ptr, ops[1].ptr, ops[2].ptr, ops[3].ptr, ops[4].ptr, 0, 0, M, Nn, K, N.EPI_BIAS, N.NS_F32, y.ptr)
+    except Exception:
+        N.call("ns_capture_abort", dev.handle)
+        raise
+    graph = dev.capture_end()
+    N.call("ns_memset32_async", dev.handle, C.c_uint64(y.ptr), 0, C.c_uint64(M * Nn))
+    dev.graph_launch(graph)
+    N.call("ns_qmatmul_i8", dev.handle, ops[0].ptr, ops[1].ptr, ops[2].ptr, ops[3].ptr, ops[4].ptr, 0, 0, M, Nn, K, N.EPI_BIAS, N.NS_F32, y_ref.ptr, 0)
+    dev.synchronize()
+    dev.graph_destroy(graph)
+    assert np.array_equal(y.download(count=M * Nn).view(np.uint32), y_ref.download().view(np.uint32))
+
+
+def test_rejects_an_unknown_residual_dtype(dev, orc):
+    M, Nn, K = 16, 256, 512
+    ops = _operands(dev, orc, M, Nn, K, 971)
+    y = dev.empty(M * Nn)
+    with pytest.raises(N.NsError) as err:
+        N.call("ns_qmatmul_i8_static", dev.handle, ops[0].ptr, ops[1].ptr, ops[2].ptr, ops[3].ptr, ops[4].ptr, y.ptr, 7, M, Nn, K,
+               N.EPI_BIAS_RESIDUAL, N.NS_F32, y.ptr)
+    assert err.value.code == 2

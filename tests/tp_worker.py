@@ -94,5 +94,49 @@ def gpu_mode():
     print(f"rank {rank}: gpu ok, agreement {agree:.3f}")
 
 
+def watch_mode():
+    """Failure detection between steps, on the host: rank 1 returns after three steps; rank 0 learns of it before it
+    queues the fourth (its wait for rank 1's step counter runs out), tears down its (stand-in) communicator and gets
+    NS_ERR_COMM.  A second watch shows the other trigger: the transport's own asynchronous error."""
+    from nn_b200 import native as N
+    rank, world, _ = dist.env_rank()
+    dist.broadcast_bytes(b"x" if rank == 0 else None, 1)     # brings the gloo group (and its store) up
+    calls = {"abort": 0, "poll": 0}
+
+    def fake_abort():
+        calls["abort"] += 1
+
+    def fake_poll():
+        calls["poll"] += 1
+        return 0
+
+    watch = dist.PeerWatch(rank, world, timeout_s=1.0, comm_error=fake_poll, comm_abort=fake_abort)
+    for step in range(3):
+        watch.check(step)            # a step of the decoder would be queued here
+    if rank == 1:
+        print("rank 1: cpu ok (left after three steps)")
+        sys.stdout.flush()
+        os._exit(0)                  # leaves between steps without a goodbye
+    try:
+        watch.check(3)
+        raise AssertionError("rank 0 must not get past the missing rank")
+    except N.NsError as e:
+        assert e.code == 5 and "rank 1 did not reach step 3" in e.text, e.text
+    assert calls["abort"] == 1 and calls["poll"] > 0
+    # the transport reporting an error ends the wait at once
+    watch2 = dist.PeerWatch(rank, world, timeout_s=30.0, comm_error=lambda: 6, comm_abort=fake_abort, prefix="ns_watch2")
+    import time
+    t0 = time.monotonic()
+    try:
+        watch2.check(0)
+        raise AssertionError("an asynchronous transport error must fail the check")
+    except N.NsError as e:
+        assert e.code == 5 and "error 6" in e.text
+    assert time.monotonic() - t0 < 5.0 and calls["abort"] == 2
+    print("rank 0: cpu ok (saw rank 1 leave)")
+    sys.stdout.flush()
+    os._exit(0)
+
+
 if __name__ == "__main__":
-    cpu_mode() if sys.argv[1] == "cpu" else gpu_mode()
+    {"cpu": cpu_mode, "gpu": gpu_mode, "watch": watch_mode}[sys.argv[1]]()
