@@ -206,5 +206,6 @@ def test_equals_the_reference_float_linear_on_dequantised_operands(dev, orc, M):
     bound = K * 2.0 ** -23 * magnitude
     err = np.abs(ref.astype(np.float64) - y.astype(np.float64))
     assert np.all(err <= bound), f"largest excess {float((err - bound).max()):.3e}"
-    # and the bound is not vacuous: it is far below the spread of the outputs
-    assert float(bound.max()) < 1e-2 * float(np.abs(ref).mean())
+    # that worst-case bound is loose (a few per cent of a typical output); the float-accumulation bar of the benchmark
+    # configuration, 1e-4 with the reference's rule |e - a| <= tol * max(1, |e|), holds as well
+    assert orc.close(ref[0], y, 1e-4), f"max err {orc.max_err(ref[0], y):.3e}"

@@ -3,11 +3,14 @@ of benchmark configuration 5 (same head_dim 128 and operator sequence, fewer/nar
 
 Protocol (greedy argmax can flip on near-ties under reordered arithmetic): teacher-forced per-step comparison of the
 logits and of the argmax wherever the oracle's top-2 gap exceeds the tolerance.  Every operator is held to its own
-bar in its own test (int32 accumulators bit-exact, bf16 outputs 1e-2); end to end the differences compound: a value
-that lands on the other side of a bf16 or int8 rounding boundary (flash attention rounds P to bf16, LayerNorm sums in
-another order) moves one quantisation step, and each of the 4 * layers + 1 quantised products passes that on.  The
-logits are therefore compared with 5e-2 * max(1, |e|); then a free-running generation through the CUDA graph, which must reproduce the teacher-forced run's
-tokens exactly (GraphReplay, DecodingTests.cs:144-189) and hit the context reset of CharGpt.cs:276-283.
+bar in its own test (int32 accumulators bit-exact, bf16 outputs 1e-2).  End to end the integer sums are exact and the
+float epilogues run in the oracle's order; what differs (softmax and LayerNorm summation order, exp2 / tanh
+approximations) is far below a bf16 ulp and is absorbed by the rounding to bf16 and then to int8 that follows every
+operator -- unless a value sits on a rounding boundary, which moves one quantisation step of one product input.  On the
+configurations below no such flip occurs: the logits come out bit-identical (largest error printed by the test: 0).
+The bar is therefore the benchmark configuration's bf16 tolerance, 1e-2 * max(1, |e|); then a free-running generation through the
+CUDA graph, which must reproduce the teacher-forced run's tokens exactly (GraphReplay, DecodingTests.cs:144-189) and
+hit the context reset of CharGpt.cs:276-283.
 """
 import ctypes as C
 
@@ -19,7 +22,7 @@ from nn_b200.gpt import GptConfig, GptW8A8
 from oracle import model as om
 
 pytestmark = pytest.mark.gpu
-TOL = 5e-2
+TOL = 1e-2
 
 
 WORST = {"err": 0.0}
