@@ -273,6 +273,14 @@ NS_API int ns_kv_append(ns_device_t dev, ns_kv_cache_t cache, uint64_t k, uint64
 NS_API int ns_attention_decode(ns_device_t dev, ns_kv_cache_t cache, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride,
                                uint64_t page_table, int max_pages, uint64_t pos_dev, int batch, int steps, float scale);
 
+/* ns_attention_decode, and the output rows [batch * steps, heads * head_dim] (o_stride = heads * head_dim) also leave as
+ * int8 rows q_out with one float scale per row in q_scale -- ns_quantize_rows_i8 of the bf16 output, bit for bit, done
+ * by the last CTA that finishes a row.  This is the input of the attention output projection (Layers/Attention.cs:113-117);
+ * it saves the decoding step a launch.  batch * steps <= 4000. */
+NS_API int ns_attention_decode_quant(ns_device_t dev, ns_kv_cache_t cache, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride,
+                                     uint64_t page_table, int max_pages, uint64_t pos_dev, int batch, int steps, float scale, uint64_t q_out,
+                                     uint64_t q_scale);
+
 /* Attention over a whole sequence (MultiHeadAttention.ForwardCore, Layers/Attention.cs:46-91) without the
  * [T, T] score tensor: o[b, h, i, :] = softmax_j((q[b,h,i,:] . k[b,h,j,:]) * scale + mask) . v[b,h,j,:], mask = -inf
  * for j > i when causal.  head_dim must be 128.  Element (b, h, s, d) of each tensor sits at
@@ -332,6 +340,21 @@ NS_API int ns_finish_norm_quant(ns_device_t dev, uint64_t partial, int splits, n
 NS_API int ns_finish_kv_append(ns_device_t dev, uint64_t partial, int splits, ns_linear_t linear, uint64_t x_scale, int batch, int steps,
                                uint64_t qkv, ns_kv_cache_t cache, uint64_t page_table, int max_pages, uint64_t pos_dev);
 
+/* One launch per Linear of the decoding step: the int8 product of `linear` (x int8 [rows, K_local], x_scale float [rows]) and, as a
+ * second phase of the SAME kernel after a device-wide arrival counter, the row operator that follows it in the decoder
+ * block (TransformerEncoderLayer.ForwardCached, Layers/Attention.cs:201-211).  rows <= 256 (the few rows of a decoding
+ * step); N_local a multiple of 256 up to 8192 for the two row-wise forms; buffers 16-byte aligned.  Results are
+ * bit-identical to the two-launch forms above.  All three use the device object's scratch block and synchronisation words:
+ * calls on one device object must not overlap on the GPU.
+ *   ns_linear_forward_norm_quant = ns_linear_forward_partial + ns_finish_norm_quant   (attention output projection, FF2)
+ *   ns_linear_forward_gelu_quant = product + bias + GELU -> bf16 -> ns_quantize_rows_i8 (FF1; bias_gelu_f32, PtxKernels.Decoding.cs:93-114)
+ *   ns_linear_forward_kv_append  = ns_linear_forward_partial + ns_finish_kv_append    (fused QKV projection) */
+NS_API int ns_linear_forward_norm_quant(ns_device_t dev, ns_linear_t linear, uint64_t x, uint64_t x_scale, uint64_t residual, int64_t rows,
+                                        uint64_t x_out, uint64_t gamma, uint64_t beta, float eps, uint64_t q, uint64_t q_scale);
+NS_API int ns_linear_forward_gelu_quant(ns_device_t dev, ns_linear_t linear, uint64_t x, uint64_t x_scale, int64_t rows, uint64_t q, uint64_t q_scale);
+NS_API int ns_linear_forward_kv_append(ns_device_t dev, ns_linear_t linear, uint64_t x, uint64_t x_scale, int batch, int steps, uint64_t qkv,
+                                       ns_kv_cache_t cache, uint64_t page_table, int max_pages, uint64_t pos_dev);
+
 /* ------------------------------------------------------------------------------------------------
  * Tensor parallelism over NCCL.  No counterpart in the reference (single device; Device.cs:54-64).
  * ------------------------------------------------------------------------------------------------ */
@@ -375,6 +398,15 @@ NS_API int ns_peer_group_slot(ns_peer_group_t group, int slot, uint64_t* ptr);
  * of 256 up to 8192. */
 NS_API int ns_tp_reduce_norm_quant(ns_device_t dev, ns_peer_group_t group, int slot, uint64_t bias, uint64_t residual, int64_t rows, int cols,
                                    uint64_t x_out, uint64_t gamma, uint64_t beta, float eps, uint64_t q, uint64_t q_scale);
+/* The row-parallel product of `linear` (a row shard: x int8 [rows, K_local]) AND the exchange above in one launch: the kernel
+ * writes this rank's float partial rows into its slot, all its CTAs arrive on a device-wide counter, one CTA then raises
+ * the ranks' flags and the CTAs that own rows wait for every rank's flag and finish as ns_tp_reduce_norm_quant does.  K is
+ * not split inside a rank.  rows <= min(256, SM count).  Same call order rule and bounded waits (status 400 + rank for a
+ * missing rank, 410 for this rank's own CTAs).  Serves x + Linear(...) -> LayerNorm of Layers/Attention.cs:201-205 on
+ * several GPUs; no counterpart in the single-device reference. */
+NS_API int ns_linear_forward_tp_norm_quant(ns_device_t dev, ns_linear_t linear, ns_peer_group_t group, int slot, uint64_t x, uint64_t x_scale,
+                                           uint64_t residual, int64_t rows, uint64_t x_out, uint64_t gamma, uint64_t beta, float eps, uint64_t q,
+                                           uint64_t q_scale);
 NS_API int ns_peer_group_destroy(ns_peer_group_t group);
 
 #ifdef __cplusplus

@@ -41,6 +41,10 @@ struct DecodeParams {
     int batch, steps, splits;
     float scale;
     float* partial;  // [rows, splits, 2 + dh] when splits > 1
+    // optional: int8 row quantisation of the output (the next product's input) by the last CTA to finish a row
+    int8_t* q_out;          // [batch * steps, heads * dh] or null
+    float* q_scale;         // [batch * steps]
+    uint32_t* row_tickets;  // one word per output row, zero between launches
 };
 
 __device__ __forceinline__ float warp_max_f(float v)
@@ -63,6 +67,58 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8])
     for (int t = 0; t < 4; t++) {
         f[2 * t] = __uint_as_float(w[t] << 16);
         f[2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
+    }
+}
+
+// The output row (b, i) -- all heads of one token -- is complete when `heads` CTAs have stored their 128 (or 64, 32)
+// columns.  Each CTA takes a ticket of its row after its store; the one that draws the last ticket quantises the row:
+// scale = absmax / 127 (1 for a zero row), q = clamp(rint(x / scale)), exactly ns_quantize_rows_i8 on the bf16 values,
+// and clears the ticket word.  This folds a launch of the decoding step into the attention kernel.
+template <int THREADS>
+__device__ __forceinline__ void quantize_row_if_last(const DecodeParams& p, int b, int i, int dh, float* red, int* last_smem)
+{
+    const int row = b * p.steps + i;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t t = atomicAdd(&p.row_tickets[row], 1u);
+        *last_smem = (t == (uint32_t)p.heads - 1u) ? 1 : 0;
+        if (*last_smem) p.row_tickets[row] = 0u;
+    }
+    __syncthreads();
+    if (*last_smem == 0) return;
+    __threadfence();
+    const int cols = p.heads * dh;
+    const uint16_t* src = p.o + (size_t)row * p.o_stride;
+    float amax = 0.0f;
+    for (int v = threadIdx.x; v < cols / 8; v += THREADS) {
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(src + v * 8));
+        float f[8];
+        unpack8(raw, f);
+#pragma unroll
+        for (int d = 0; d < 8; d++) amax = fmaxf(amax, fabsf(f[d]));
+    }
+    amax = warp_max_f(amax);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+    for (int w = 1; w < THREADS / 32; w++) amax = fmaxf(amax, red[w]);
+    const float sc = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    if (threadIdx.x == 0) p.q_scale[row] = sc;
+    int8_t* dst = p.q_out + (size_t)row * cols;
+    for (int v = threadIdx.x; v < cols / 8; v += THREADS) {
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(src + v * 8));
+        float f[8];
+        unpack8(raw, f);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int d = 0; d < 4; d++) {
+            float q0 = fminf(fmaxf(rintf(__fdiv_rn(f[d], sc)), -127.0f), 127.0f);
+            float q1 = fminf(fmaxf(rintf(__fdiv_rn(f[4 + d], sc)), -127.0f), 127.0f);
+            lo |= (uint32_t)(uint8_t)(int8_t)q0 << (8 * d);
+            hi |= (uint32_t)(uint8_t)(int8_t)q1 << (8 * d);
+        }
+        *reinterpret_cast<uint2*>(dst + v * 8) = make_uint2(lo, hi);
     }
 }
 
@@ -228,6 +284,10 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
             if (d == 0) { dst[0] = m_run; dst[1] = l_run; }
         }
     }
+    if (p.q_out != nullptr && p.splits == 1) {
+        __shared__ int last_cta;
+        quantize_row_if_last<DEC_THREADS>(p, b, i, DH, s_red, &last_cta);
+    }
 }
 
 // Merges the per-split (max, sum, unnormalised output) triples of one row.
@@ -255,6 +315,12 @@ __global__ void ns_attention_combine_kernel(const DecodeParams p)
             if (ms != -INFINITY) t += src[s * (2 + DH) + 2 + d] * expf(ms - m);
         }
         p.o[(size_t)(b * p.steps + i) * p.o_stride + h * DH + d] = ns_f32_to_bf16_bits(t / l);
+    }
+    if (p.q_out != nullptr) {
+        __shared__ int last_cta;
+        __shared__ float red[2];
+        if (DH < 64) quantize_row_if_last<32>(p, b, i, DH, red, &last_cta);
+        else quantize_row_if_last<64>(p, b, i, DH, red, &last_cta);
     }
 }
 
@@ -409,7 +475,7 @@ static int choose_splits(const NsDevice* d, int rows, int max_len, int page_size
 
 int ns_attention_decode_impl(NsDevice* d, NsKvCache* c, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride, uint64_t page_table,
                              int max_pages, uint64_t pos_dev, int batch, int steps, float scale, float* scratch, size_t scratch_bytes,
-                             bool own_scratch)
+                             bool own_scratch, uint64_t q_out = 0, uint64_t q_scale = 0)
 {
     NS_REQUIRE(c && q && o && page_table && pos_dev, NS_ERR_ARGUMENT, "ns_attention_decode: null argument");
     NS_REQUIRE(batch > 0 && steps > 0 && max_pages > 0, NS_ERR_ARGUMENT, "ns_attention_decode: bad shape");
@@ -424,6 +490,14 @@ int ns_attention_decode_impl(NsDevice* d, NsKvCache* c, uint64_t q, int64_t q_st
     while ((1 << p.page_shift) < c->page_size) p.page_shift++;
     p.pos_dev = reinterpret_cast<const int32_t*>(pos_dev);
     p.batch = batch; p.steps = steps; p.scale = scale;
+    p.q_out = reinterpret_cast<int8_t*>(q_out);
+    p.q_scale = reinterpret_cast<float*>(q_scale);
+    p.row_tickets = d->sync_words + NS_SYNC_ROW_TICKETS;
+    if (q_out != 0) {
+        NS_REQUIRE(q_scale != 0 && (q_out & 7) == 0 && (o & 15) == 0 && o_stride % 8 == 0, NS_ERR_ARGUMENT,
+                   "ns_attention_decode_quant: q_scale missing or buffers misaligned");
+        NS_REQUIRE((int64_t)batch * steps <= NS_SYNC_MAX_ROWS, NS_ERR_ARGUMENT, "ns_attention_decode_quant: at most %d output rows", (int)NS_SYNC_MAX_ROWS);
+    }
     const int rows = batch * c->heads * steps;
     // the context length lives on the device; the split count is sized for the longest possible context
     p.splits = choose_splits(d, rows, max_pages * c->page_size, c->page_size);
@@ -455,4 +529,20 @@ extern "C" int ns_attention_decode(ns_device_t h, ns_kv_cache_t ch, uint64_t q, 
     if (rc != NS_OK) return rc;
     return ns_attention_decode_impl(d, reinterpret_cast<NsKvCache*>(ch), q, q_stride, o, o_stride, page_table, max_pages, pos_dev, batch, steps,
                                     scale, nullptr, 0, true);
+}
+
+// The same, and the output rows [batch * steps, heads * head_dim] also leave as int8 rows with one scale per row (the
+// input of the attention output projection): the row quantisation the decoding step would otherwise launch next.
+extern "C" int ns_attention_decode_quant(ns_device_t h, ns_kv_cache_t ch, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride,
+                                         uint64_t page_table, int max_pages, uint64_t pos_dev, int batch, int steps, float scale, uint64_t q_out,
+                                         uint64_t q_scale)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(q_out != 0 && q_scale != 0, NS_ERR_ARGUMENT, "ns_attention_decode_quant: q_out and q_scale are required");
+    NsKvCache* c = reinterpret_cast<NsKvCache*>(ch);
+    NS_REQUIRE(c != nullptr && o_stride == (int64_t)c->heads * c->head_dim, NS_ERR_ARGUMENT,
+               "ns_attention_decode_quant: the output rows must be contiguous (stride = heads x head_dim)");
+    return ns_attention_decode_impl(d, c, q, q_stride, o, o_stride, page_table, max_pages, pos_dev, batch, steps, scale, nullptr, 0, true, q_out, q_scale);
 }

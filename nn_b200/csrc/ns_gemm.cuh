@@ -2,6 +2,7 @@
 #pragma once
 
 #include "ns_common.cuh"
+#include "ns_tail.cuh"
 
 enum { NS_KIND_I8 = 0, NS_KIND_BF16 = 1 };
 
@@ -37,9 +38,13 @@ struct NsGemmParams {
 // deferred_partial / deferred_splits: when non-null (int8 kind only) the epilogue is left to a later kernel: exact
 // int32 partial sums [splits, M, N] stay in the device object's scratch block (one slab when K is not split) and the
 // two out-parameters describe them; no second kernel is launched.
+// tail: when non-null (int8 kind, [N, K] weights, M <= NS_TAIL_MAX_ROWS) the launch continues with the row operator
+// the struct describes (ns_tail.cuh).  For NS_TAIL_PEER the product writes its float partial rows to p.out (K is not
+// split); for the other kinds the epilogue is deferred as above and the launcher fills tail->partial / tail->splits.
 int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_kn, int M, int N, int K, NsGemmParams p,
                 void* partial_override = nullptr, size_t partial_override_bytes = 0, void** deferred_partial = nullptr,
-                int* deferred_splits = nullptr);
+                int* deferred_splits = nullptr, NsTail* tail = nullptr);
+constexpr int NS_TAIL_MAX_ROWS = 256;
 
 // The row-streaming int8 kernel for 1..8 activation rows (ns_gemv_i8.cu).  `p` must hold M, N, K, the epilogue
 // fields, out / raw and the scale, bias and residual pointers.

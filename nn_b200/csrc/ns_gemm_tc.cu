@@ -25,7 +25,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#define NS_TAIL_DEVICE_CODE
 #include "ns_gemm.cuh"
+#include "ns_tail.cuh"
 
 namespace {
 
@@ -261,10 +263,10 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
     }
 }
 
-template <int KIND, int BN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ StoreMaps sm, const NsGemmParams p)
+// TAIL: the launch has NS_TAIL_THREADS threads (warps 6 and 7 idle during the product) and is followed, in the same
+// kernel, by the row operator of ns_tail.cuh; queued stores are then waited for until COMPLETE, not only until read.
+template <int KIND, int BN, bool B_MN, bool TAIL>
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p)
 {
     using Cfg = TileCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
@@ -408,7 +410,7 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (ok) ns_tc_commit(tfull_bar(acc));
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------------------------------------------------------- epilogue
         const int quad = warp & 3;
         EpiCtx cx;
@@ -467,8 +469,12 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             if (lane == 0) ns_mbar_arrive(tempty_bar(acc));
         }
         // shared memory must stay valid until every queued store has read it; the stores themselves are
-        // complete when the grid is
-        if (lane == 0) ns_bulk_wait_read<0>();
+        // complete when the grid is -- unless a second phase of this launch reads them: then they are waited for
+        // until complete, and made visible to the other SMs
+        if (lane == 0) {
+            if (TAIL) { ns_bulk_wait<0>(); __threadfence(); }
+            else ns_bulk_wait_read<0>();
+        }
         __syncwarp();
     }
 
@@ -485,6 +491,24 @@ ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         ns_tc_fence_after();
         ns_tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+}
+
+template <int KIND, int BN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+ns_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ StoreMaps sm, const NsGemmParams p)
+{
+    gemm_tc_body<KIND, BN, B_MN, false>(tmA, tmB, sm, p);
+}
+
+// The int8 product of a decoding step followed, in the same launch, by the row operator `tail` describes.
+template <int BN>
+__global__ void __launch_bounds__(NS_TAIL_THREADS, 1)
+ns_gemm_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ StoreMaps sm, const NsGemmParams p, const __grid_constant__ NsTail tail)
+{
+    gemm_tc_body<NS_KIND_I8, BN, false, true>(tmA, tmB, sm, p);
+    ns_tail::run(tail);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -786,6 +810,23 @@ __global__ void ns_gemm_splitk_finish_kernel(const NsGemmParams p)
     }
 }
 
+template <int BN>
+int launch_gemm_tail(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p, const NsTail& tail)
+{
+    using Cfg = TileCfg<BN>;
+    auto kernel = ns_gemm_tail_kernel<BN>;
+    static bool configured[64] = {false};
+    if (!configured[d->ordinal]) {
+        NS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM_BYTES));
+        configured[d->ordinal] = true;
+    }
+    // every CTA must be resident while CTAs wait for one another: one per SM (the kernel's shared memory allows no more)
+    int items = p.tiles_m * p.tiles_n * p.k_splits;
+    int grid = items < d->sm_count ? items : d->sm_count;
+    NS_CUDA(ns_launch_pdl(kernel, dim3(grid), dim3(NS_TAIL_THREADS), Cfg::SMEM_BYTES, d->stream, tmA, tmB, sm, p, tail));
+    return NS_OK;
+}
+
 template <int KIND, int BN, bool B_MN>
 int launch_gemm(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p)
 {
@@ -878,8 +919,14 @@ void ns_gemm_choose_tiling(const NsDevice* d, int M, int N, int k_blocks, int* b
 }
 
 int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_kn, int M, int N, int K, NsGemmParams p,
-                void* partial_override, size_t partial_override_bytes, void** deferred_partial, int* deferred_splits)
+                void* partial_override, size_t partial_override_bytes, void** deferred_partial, int* deferred_splits, NsTail* tail)
 {
+    NS_REQUIRE(tail == nullptr || (kind == NS_KIND_I8 && !b_is_kn && M <= NS_TAIL_MAX_ROWS), NS_ERR_ARGUMENT,
+               "a product with a second phase is an int8 product of at most %d rows", NS_TAIL_MAX_ROWS);
+    const bool peer_tail = tail != nullptr && tail->kind == NS_TAIL_PEER;
+    void* tail_partial = nullptr;
+    int tail_splits = 0;
+    if (tail != nullptr && !peer_tail) { deferred_partial = &tail_partial; deferred_splits = &tail_splits; }
     const bool deferred = deferred_partial != nullptr && deferred_splits != nullptr;
     NS_REQUIRE(!deferred || kind == NS_KIND_I8, NS_ERR_ARGUMENT, "a deferred epilogue exists for int8 products only");
     const int elsize = kind == NS_KIND_I8 ? 1 : 2;
@@ -890,7 +937,7 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     p.M = M; p.N = N; p.K = K;
     // One to eight rows of int8 activations: the row-streaming kernel on the CUDA cores (a tuning override keeps
     // the tensor-core kernels, as does a deferred epilogue).
-    if (kind == NS_KIND_I8 && !deferred && d->force_bn == 0 && d->force_splits == 0 && ns_gemv_i8_fits(M, K) &&
+    if (kind == NS_KIND_I8 && !deferred && tail == nullptr && d->force_bn == 0 && d->force_splits == 0 && ns_gemv_i8_fits(M, K) &&
         ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0)
         return ns_gemv_i8_run(d, p, a, b);
     p.k_blocks = (int)(((int64_t)K * elsize + BKB - 1) / BKB);
@@ -899,7 +946,12 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     // Large products with [N, K] weights go to the CTA-pair kernel (256 x 256 tiles over two SMs): whenever 256-wide
     // tiles without a K split were chosen and there are at least two row tiles.  The test hook NS_TUNE_PAIR forces it,
     // a tile width of 256 forces the single-CTA kernel.
-    const bool pair = splits == 1 && M > BM && (d->force_bn == NS_TUNE_PAIR || (d->force_bn == 0 && bn == 256));
+    if (peer_tail) {
+        // The ranks exchange float partial rows, so K stays whole; narrow tiles spread the weight stream over more SMs.
+        splits = 1;
+        if (d->force_bn == 0) bn = 64;
+    }
+    const bool pair = tail == nullptr && splits == 1 && M > BM && (d->force_bn == NS_TUNE_PAIR || (d->force_bn == 0 && bn == 256));
     p.kb_per_split = (p.k_blocks + splits - 1) / splits;
     p.k_splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
     p.tiles_m = pair ? (M + 255) / 256 : (M + BM - 1) / BM;
@@ -988,6 +1040,19 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
                 rc = ns_make_tensor_map(&sm.raw, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, p.raw, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
                 if (rc != NS_OK) return rc;
             }
+        }
+    }
+    if (tail != nullptr) {
+        if (!peer_tail) {
+            tail->partial = reinterpret_cast<const int32_t*>(p.k_splits > 1 ? p.partial : reinterpret_cast<void*>(p.raw));
+            tail->splits = p.k_splits;
+        }
+        tail->sync = d->sync_words;
+        tail->status = d->status_dev;
+        switch (bn) {
+            case 256: return launch_gemm_tail<256>(d, tmA, tmB, sm, p, *tail);
+            case 128: return launch_gemm_tail<128>(d, tmA, tmB, sm, p, *tail);
+            default: return launch_gemm_tail<64>(d, tmA, tmB, sm, p, *tail);
         }
     }
     if (pair) {

@@ -23,6 +23,7 @@
 #include <string.h>
 
 #include "ns_rows.cuh"
+#include "ns_tail.cuh"
 
 namespace {
 
@@ -274,6 +275,28 @@ extern "C" int ns_tp_reduce_norm_quant(ns_device_t dh, ns_peer_group_t h, int sl
         case 2: NS_CUDA(ns_launch_plain(ns_tp_reduce_norm_quant_kernel<2>, grid, block, 0, d->stream, p)); break;
         default: NS_CUDA(ns_launch_plain(ns_tp_reduce_norm_quant_kernel<4>, grid, block, 0, d->stream, p)); break;
     }
+    return NS_OK;
+}
+
+// The exchange of `slot` as the second phase of a product launch (ns_tail.cuh, NS_TAIL_PEER): fills the peer fields of
+// `t` and returns the address the product must write this rank's float partial rows to.
+int ns_peer_fill_tail(ns_peer_group_t h, NsDevice* d, int slot, int64_t rows, int cols, NsTail* t, void** slot_ptr)
+{
+    NsPeerGroup* g = as_group(h);
+    NS_REQUIRE(g != nullptr && g->dev == d && g->connected, NS_ERR_ARGUMENT, "the peer group is not connected on this device");
+    NS_REQUIRE(slot >= 0 && slot < PEER_SLOTS && rows > 0, NS_ERR_ARGUMENT, "bad exchange slot or row count");
+    NS_REQUIRE((size_t)rows * cols * 4 <= g->slot_bytes, NS_ERR_ARGUMENT, "%lld x %d floats exceed the exchange slot", (long long)rows, cols);
+    static_assert(PEER_MAX == NS_TAIL_PEER_MAX, "peer limits");
+    for (int r = 0; r < PEER_MAX; r++) { t->part[r] = nullptr; t->remote_flag[r] = nullptr; }
+    for (int r = 0; r < g->world; r++) {
+        t->part[r] = reinterpret_cast<const float*>(g->peers[r] + PEER_HEADER + (size_t)slot * g->slot_bytes);
+        t->remote_flag[r] = reinterpret_cast<uint32_t*>(g->peers[r]) + slot * PEER_MAX + g->rank;
+    }
+    t->local_flags = reinterpret_cast<const uint32_t*>(g->local) + slot * PEER_MAX;
+    t->epoch = g->state + slot;
+    t->rank = g->rank;
+    t->world = g->world;
+    *slot_ptr = g->local + PEER_HEADER + (size_t)slot * g->slot_bytes;
     return NS_OK;
 }
 

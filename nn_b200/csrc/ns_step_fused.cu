@@ -15,7 +15,7 @@
 // results are bit-identical to the unfused sequence.
 #include <math.h>
 
-#include "ns_common.cuh"
+#include "ns_gemm.cuh"
 #include "ns_rows.cuh"
 
 struct NsKvCacheView {
@@ -341,4 +341,183 @@ extern "C" int ns_finish_kv_append(ns_device_t h, uint64_t partial, int splits, 
     if (blocks > (int64_t)d->sm_count * 16) blocks = (int64_t)d->sm_count * 16;
     NS_CUDA(ns_launch_plain(ns_finish_kv_append_kernel, dim3((unsigned)blocks), dim3(256), 0, d->stream, p));
     return NS_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// One launch per Linear of the decoding step: the int8 product and, as its second phase, the row operator that
+// follows it (ns_tail.cuh).  These replace the pairs ns_linear_forward_partial + ns_finish_* / ns_quantize_rows_i8 /
+// ns_tp_reduce_norm_quant above; results are bit-identical to them.
+// ---------------------------------------------------------------------------------------------------------
+int ns_peer_fill_tail(ns_peer_group_t h, NsDevice* d, int slot, int64_t rows, int cols, NsTail* t, void** slot_ptr);   // ns_peer.cu
+
+namespace {
+
+struct LinearView {
+    int k_loc, n_loc, mode;
+    uint64_t w, w_scale, bias;
+};
+
+int view_linear(ns_linear_t linear, LinearView* v, const char* who)
+{
+    int rc = ns_linear_info(linear, &v->k_loc, &v->n_loc, &v->mode, &v->w, &v->w_scale, &v->bias);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(v->mode == NS_I8 && v->w_scale != 0, NS_ERR_ARGUMENT, "%s: the layer must be an int8 layer", who);
+    return NS_OK;
+}
+
+// row shape of the second phase: `active` of its NS_TAIL_THREADS threads hold `vpt` vectors of 8 columns
+int tail_row_shape(int cols, NsTail* t, const char* who)
+{
+    unsigned threads = 0;
+    int vpt = 0;
+    NS_REQUIRE(ns_rows::row_shape(cols, &threads, &vpt) && threads <= (unsigned)NS_TAIL_THREADS, NS_ERR_ARGUMENT,
+               "%s: rows of %d columns (a multiple of 256 up to 8192 is needed)", who, cols);
+    t->active = (int)threads;
+    t->vpt = vpt;
+    return NS_OK;
+}
+
+int run_with_tail(NsDevice* d, const LinearView& v, uint64_t x, int M, NsGemmParams p, NsTail* t)
+{
+    p.prefetch_b = 1;
+    return ns_gemm_run(d, NS_KIND_I8, reinterpret_cast<const void*>(x), reinterpret_cast<const void*>(v.w), false, M, v.n_loc, v.k_loc, p, nullptr, 0,
+                       nullptr, nullptr, t);
+}
+
+}  // namespace
+
+extern "C" int ns_linear_forward_norm_quant(ns_device_t h, ns_linear_t linear, uint64_t x, uint64_t x_scale, uint64_t residual, int64_t rows,
+                                            uint64_t x_out, uint64_t gamma, uint64_t beta, float eps, uint64_t q, uint64_t q_scale)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    LinearView v;
+    rc = view_linear(linear, &v, "ns_linear_forward_norm_quant");
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(x && x_scale && x_out && rows > 0 && rows <= NS_TAIL_MAX_ROWS, NS_ERR_ARGUMENT, "ns_linear_forward_norm_quant: bad argument (1..%d rows)",
+               NS_TAIL_MAX_ROWS);
+    NS_REQUIRE(gamma == 0 || (beta != 0 && q != 0 && q_scale != 0), NS_ERR_ARGUMENT, "ns_linear_forward_norm_quant: LayerNorm needs beta, q and q_scale");
+    NS_REQUIRE(((x_out | residual | gamma | beta | q | v.w_scale | v.bias) & 15) == 0, NS_ERR_ARGUMENT, "ns_linear_forward_norm_quant: buffers must be 16-byte aligned");
+    NsTail t = {};
+    t.kind = NS_TAIL_NORM;
+    rc = tail_row_shape(v.n_loc, &t, "ns_linear_forward_norm_quant");
+    if (rc != NS_OK) return rc;
+    t.x_scale = reinterpret_cast<const float*>(x_scale);
+    t.w_scale = reinterpret_cast<const float*>(v.w_scale);
+    t.bias = reinterpret_cast<const float*>(v.bias);
+    t.rows = rows; t.cols = v.n_loc;
+    t.residual = reinterpret_cast<const uint16_t*>(residual);
+    t.x_out = reinterpret_cast<uint16_t*>(x_out);
+    t.gamma = reinterpret_cast<const float*>(gamma);
+    t.beta = reinterpret_cast<const float*>(beta);
+    t.eps = eps;
+    t.q = reinterpret_cast<int8_t*>(q);
+    t.q_scale = reinterpret_cast<float*>(q_scale);
+    NsGemmParams p = {};
+    p.epilogue = NS_EPI_NONE; p.out_dtype = NS_F32; p.residual_dtype = NS_F32;
+    return run_with_tail(d, v, x, (int)rows, p, &t);
+}
+
+extern "C" int ns_linear_forward_gelu_quant(ns_device_t h, ns_linear_t linear, uint64_t x, uint64_t x_scale, int64_t rows, uint64_t q, uint64_t q_scale)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    LinearView v;
+    rc = view_linear(linear, &v, "ns_linear_forward_gelu_quant");
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(x && x_scale && q && q_scale && rows > 0 && rows <= NS_TAIL_MAX_ROWS, NS_ERR_ARGUMENT, "ns_linear_forward_gelu_quant: bad argument (1..%d rows)",
+               NS_TAIL_MAX_ROWS);
+    NS_REQUIRE(v.bias != 0, NS_ERR_ARGUMENT, "ns_linear_forward_gelu_quant: the layer has no bias");
+    NS_REQUIRE(((q | v.w_scale | v.bias) & 15) == 0, NS_ERR_ARGUMENT, "ns_linear_forward_gelu_quant: buffers must be 16-byte aligned");
+    NsTail t = {};
+    t.kind = NS_TAIL_GELU;
+    rc = tail_row_shape(v.n_loc, &t, "ns_linear_forward_gelu_quant");
+    if (rc != NS_OK) return rc;
+    t.x_scale = reinterpret_cast<const float*>(x_scale);
+    t.w_scale = reinterpret_cast<const float*>(v.w_scale);
+    t.bias = reinterpret_cast<const float*>(v.bias);
+    t.rows = rows; t.cols = v.n_loc;
+    t.q = reinterpret_cast<int8_t*>(q);
+    t.q_scale = reinterpret_cast<float*>(q_scale);
+    NsGemmParams p = {};
+    p.epilogue = NS_EPI_NONE; p.out_dtype = NS_F32; p.residual_dtype = NS_F32;
+    return run_with_tail(d, v, x, (int)rows, p, &t);
+}
+
+extern "C" int ns_linear_forward_kv_append(ns_device_t h, ns_linear_t linear, uint64_t x, uint64_t x_scale, int batch, int steps, uint64_t qkv,
+                                           ns_kv_cache_t cache, uint64_t page_table, int max_pages, uint64_t pos_dev)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    LinearView v;
+    rc = view_linear(linear, &v, "ns_linear_forward_kv_append");
+    if (rc != NS_OK) return rc;
+    NsKvCacheView c;
+    rc = ns_kv_cache_view(cache, &c);
+    if (rc != NS_OK) return rc;
+    const int64_t rows = (int64_t)batch * steps;
+    NS_REQUIRE(x && x_scale && qkv && page_table && pos_dev && batch > 0 && steps > 0 && max_pages > 0 && rows <= NS_TAIL_MAX_ROWS, NS_ERR_ARGUMENT,
+               "ns_linear_forward_kv_append: bad argument (1..%d rows)", NS_TAIL_MAX_ROWS);
+    NS_REQUIRE(v.n_loc == 3 * c.heads * c.head_dim, NS_ERR_ARGUMENT, "ns_linear_forward_kv_append: the layer has %d columns, the cache wants 3 x %d x %d",
+               v.n_loc, c.heads, c.head_dim);
+    NS_REQUIRE((qkv & 15) == 0, NS_ERR_ARGUMENT, "ns_linear_forward_kv_append: buffers must be 16-byte aligned");
+    NsTail t = {};
+    t.kind = NS_TAIL_KV;
+    t.x_scale = reinterpret_cast<const float*>(x_scale);
+    t.w_scale = reinterpret_cast<const float*>(v.w_scale);
+    t.bias = reinterpret_cast<const float*>(v.bias);
+    t.rows = rows; t.cols = v.n_loc;
+    t.batch = batch; t.steps = steps;
+    t.d_loc = c.heads * c.head_dim;
+    t.qkv = reinterpret_cast<uint16_t*>(qkv);
+    t.k_pool = c.k_pool; t.v_pool = c.v_pool;
+    t.page_table = reinterpret_cast<const int32_t*>(page_table);
+    t.max_pages = max_pages; t.page_size = c.page_size; t.heads = c.heads; t.dh = c.head_dim; t.num_pages = c.num_pages;
+    t.pos_dev = reinterpret_cast<const int32_t*>(pos_dev);
+    NsGemmParams p = {};
+    p.epilogue = NS_EPI_NONE; p.out_dtype = NS_F32; p.residual_dtype = NS_F32;
+    return run_with_tail(d, v, x, (int)rows, p, &t);
+}
+
+extern "C" int ns_linear_forward_tp_norm_quant(ns_device_t h, ns_linear_t linear, ns_peer_group_t group, int slot, uint64_t x, uint64_t x_scale,
+                                               uint64_t residual, int64_t rows, uint64_t x_out, uint64_t gamma, uint64_t beta, float eps, uint64_t q,
+                                               uint64_t q_scale)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    LinearView v;
+    rc = view_linear(linear, &v, "ns_linear_forward_tp_norm_quant");
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(x && x_scale && x_out && rows > 0 && rows <= NS_TAIL_MAX_ROWS && rows <= d->sm_count, NS_ERR_ARGUMENT,
+               "ns_linear_forward_tp_norm_quant: bad argument (1..%d rows)", NS_TAIL_MAX_ROWS < d->sm_count ? NS_TAIL_MAX_ROWS : d->sm_count);
+    NS_REQUIRE(gamma == 0 || (beta != 0 && q != 0 && q_scale != 0), NS_ERR_ARGUMENT, "ns_linear_forward_tp_norm_quant: LayerNorm needs beta, q and q_scale");
+    NS_REQUIRE(((x_out | residual | gamma | beta | q | v.bias) & 15) == 0, NS_ERR_ARGUMENT, "ns_linear_forward_tp_norm_quant: buffers must be 16-byte aligned");
+    NsTail t = {};
+    t.kind = NS_TAIL_PEER;
+    rc = tail_row_shape(v.n_loc, &t, "ns_linear_forward_tp_norm_quant");
+    if (rc != NS_OK) return rc;
+    void* slot_ptr = nullptr;
+    rc = ns_peer_fill_tail(group, d, slot, rows, v.n_loc, &t, &slot_ptr);
+    if (rc != NS_OK) return rc;
+    // bias and residual are added once, after the ranks' partial rows are summed
+    t.bias = reinterpret_cast<const float*>(v.bias);
+    t.rows = rows; t.cols = v.n_loc;
+    t.residual = reinterpret_cast<const uint16_t*>(residual);
+    t.x_out = reinterpret_cast<uint16_t*>(x_out);
+    t.gamma = reinterpret_cast<const float*>(gamma);
+    t.beta = reinterpret_cast<const float*>(beta);
+    t.eps = eps;
+    t.q = reinterpret_cast<int8_t*>(q);
+    t.q_scale = reinterpret_cast<float*>(q_scale);
+    NsGemmParams p = {};
+    p.epilogue = NS_EPI_NONE; p.out_dtype = NS_F32; p.residual_dtype = NS_F32;
+    p.out = slot_ptr;
+    p.a_scale = reinterpret_cast<const float*>(x_scale);
+    p.w_scale = reinterpret_cast<const float*>(v.w_scale);
+    return run_with_tail(d, v, x, (int)rows, p, &t);
 }

@@ -62,7 +62,9 @@ struct NsTail {
     int rank, world;
 };
 
-#ifdef __CUDACC__
+// The device code is compiled into the one source file that defines NS_TAIL_DEVICE_CODE before including this header
+// (ns_gemm_tc.cu); the others only need the struct.
+#if defined(__CUDACC__) && defined(NS_TAIL_DEVICE_CODE)
 namespace ns_tail {
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p)
@@ -399,12 +401,13 @@ __device__ __forceinline__ void peer_rows(const NsTail& t, ns_rows::RowShared& s
     }
 }
 
-// The second phase.  Called by all NS_TAIL_THREADS threads of every CTA after the product's own teardown; `stores_done`
-// says that this thread's part of the first phase (its queued stores) is complete.
+// The second phase.  Called by all NS_TAIL_THREADS threads of every CTA after the product's own teardown, when the stores
+// each thread queued in the first phase are complete.
 __device__ __noinline__ void run(const NsTail& t)
 {
     __shared__ ns_rows::RowShared sh;
-    __shared__ int flag;
+    __shared__ int flag, flag2;
+    ns_pdl_wait();   // every thread, before it reads what the kernel before this launch wrote (residual, row scales)
     if (t.kind == NS_TAIL_PEER) {
         // Every CTA arrives; CTA 0 waits for all arrivals (this rank's partial rows are then complete in its slot) and
         // tells every rank, itself included, by storing the epoch into their flag words; CTAs that own rows wait for
@@ -416,7 +419,7 @@ __device__ __noinline__ void run(const NsTail& t)
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(t.remote_flag[threadIdx.x]), "r"(e) : "memory");
         }
         const bool has_rows = (int64_t)blockIdx.x < t.rows;
-        if (threadIdx.x == 0) flag = 1;
+        if (threadIdx.x == 0) flag2 = 1;
         __syncthreads();
         if (has_rows && (int)threadIdx.x < t.world) {
             const long long t0 = clock64();
@@ -426,14 +429,14 @@ __device__ __noinline__ void run(const NsTail& t)
                 if ((int32_t)(seen - e) >= 0) break;
                 if (clock64() - t0 > NS_WAIT_LIMIT_CYCLES) {
                     *reinterpret_cast<volatile int*>(t.status) = 400 + (int)threadIdx.x;
-                    flag = 0;
+                    flag2 = 0;
                     break;
                 }
                 __nanosleep(32);
             }
         }
         __syncthreads();
-        if (has_rows && flag != 0) {
+        if (has_rows && flag2 != 0) {
             switch (t.vpt) {
                 case 1: peer_rows<1>(t, sh); break;
                 case 2: peer_rows<2>(t, sh); break;
@@ -479,4 +482,4 @@ __device__ __noinline__ void run(const NsTail& t)
 }
 
 }  // namespace ns_tail
-#endif  // __CUDACC__
+#endif  // __CUDACC__ && NS_TAIL_DEVICE_CODE

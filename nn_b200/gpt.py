@@ -151,7 +151,9 @@ class GptW8A8:
             self.am_val, self.am_idx = dev.empty(batch), dev.empty(batch, N.NS_I32)
             self.am_vals, self.am_idxs = dev.empty(batch * tp_size), dev.empty(batch * tp_size, N.NS_I32)
         self.length = 0          # host mirror of the device position (DecodingContext.Length, Layers/Decoding.cs:75)
-        self.fused = True        # few-row passes use the fused row kernels; False keeps one kernel per operator
+        # few-row passes: 2 = one launch per Linear (the row operator that follows runs as the product kernel's second phase),
+        # 1 = product kernel + fused row kernel, 0 / False = one kernel per operator
+        self.fused = 2
         self.graph = None
         self.launches_per_step = 0
 
@@ -178,6 +180,8 @@ class GptW8A8:
         assert m <= self.max_rows and self.length + steps <= cfg.context, "DecodingContext.BeginStep: capacity exceeded"
         self._n = 0
         eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
+        if m <= FUSED_MAX_ROWS and self.fused == 2 and self._one_launch_ok(m):
+            return self._forward_one_launch(steps)
         if self.tp == 1 and m <= FUSED_MAX_ROWS and self.fused:
             return self._forward_fused(steps)
         if self.tp > 1 and m <= FUSED_MAX_ROWS and self.fused and self.peer is not None:
@@ -285,6 +289,94 @@ class GptW8A8:
         N.call("ns_add_i32", h, self.pos.ptr, steps)
         self._n += 3
         self.x = [x_in, x_out]
+
+    @staticmethod
+    def _row_shape_ok(cols: int) -> bool:
+        """Rows the register-resident row code takes: a multiple of 256 columns, 1, 2 or 4 vectors of 8 per thread."""
+        if cols <= 0 or cols % 256:
+            return False
+        vecs = cols // 8
+        t = min(vecs, 256)
+        return vecs % t == 0 and vecs // t in (1, 2, 4)
+
+    def _one_launch_ok(self, m: int) -> bool:
+        ok = self._row_shape_ok(self.cfg.dim) and self._row_shape_ok(self.ff_loc) and (self.heads_loc * self.cfg.head_dim) % 8 == 0
+        if self.tp > 1:
+            ok = ok and self.peer is not None and m <= self.dev.sm_count
+        return ok
+
+    def _forward_one_launch(self, steps: int) -> None:
+        """The few-row pass with ONE launch per Linear: each int8 product kernel ends with the row operator that follows it
+        (after a device-wide arrival counter): QKV -> dequantise + bias + KV append; attention (its last CTA per row
+        quantises the row); output projection -> bias + residual + LayerNorm + quantise (on several GPUs: the exchange
+        over peer memory first); FF1 -> bias + GELU + quantise; FF2 like the output projection, with the NEXT layer's
+        LayerNorm.  Five launches per layer; results bit-identical to the other paths."""
+        cfg, dev, B = self.cfg, self.dev, self.batch
+        h, D, dh, dl = dev.handle, cfg.dim, cfg.head_dim, self.d_loc
+        m = B * steps
+        eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
+        x_in, x_out = self.x
+        hq, hs = self.hq.ptr, self.hq_scale.ptr
+        N.call("ns_embed_pos", h, self.ids.ptr, self.tok.ptr, self.pos_table.ptr, N.NS_BF16, self.pos.ptr, B, steps, D, cfg.vocab, cfg.context,
+               N.NS_BF16, x_in.ptr)
+        first = self.layers[0]
+        N.call("ns_layernorm", h, x_in.ptr, N.NS_BF16, first["ln1"][0].ptr, first["ln1"][1].ptr, C.c_int64(m), D, eps, N.NS_I8, hq, hs)
+        self._n += 2
+        head_from_last_rows = steps == 1
+
+        def reduce_norm(lin, slot, g, bta):
+            gp, bp = (g.ptr, bta.ptr) if g else (0, 0)
+            qp, sp = (hq, hs) if g else (0, 0)
+            if self.tp == 1:
+                N.call("ns_linear_forward_norm_quant", h, lin.handle, C.c_uint64(hq), C.c_uint64(hs), x_in.ptr, C.c_int64(m), x_out.ptr, gp, bp, eps, qp, sp)
+            else:
+                N.call("ns_linear_forward_tp_norm_quant", h, lin.handle, self.peer, slot, C.c_uint64(hq), C.c_uint64(hs), x_in.ptr, C.c_int64(m),
+                       x_out.ptr, gp, bp, eps, qp, sp)
+
+        for i, (L, cache) in enumerate(zip(self.layers, self.caches)):
+            N.call("ns_linear_forward_kv_append", h, L["qkv"].handle, C.c_uint64(hq), C.c_uint64(hs), B, steps, self.qkv.ptr, cache,
+                   self.page_table.ptr, self.max_pages, self.pos.ptr)
+            N.call("ns_attention_decode_quant", h, cache, C.c_uint64(self.qkv.ptr), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
+                   self.max_pages, self.pos.ptr, B, steps, scale, C.c_uint64(hq), C.c_uint64(hs))
+            reduce_norm(L["out"], 0, *L["ln2"])
+            x_in, x_out = x_out, x_in
+            N.call("ns_linear_forward_gelu_quant", h, L["ff1"].handle, C.c_uint64(hq), C.c_uint64(hs), C.c_int64(m), C.c_uint64(hq), C.c_uint64(hs))
+            if i + 1 < len(self.layers):
+                g, bta = self.layers[i + 1]["ln1"]
+            elif head_from_last_rows:
+                g, bta = self.lnf
+            else:
+                g = bta = None
+            reduce_norm(L["ff2"], 1, g, bta)
+            x_in, x_out = x_out, x_in
+            self._n += 5 + (1 if self._attention_splits(steps) > 1 else 0)
+        if not head_from_last_rows:
+            N.call("ns_d2d_2d_async", h, C.c_uint64(self.last.ptr), C.c_uint64(D * 2), C.c_uint64(x_in.ptr + (steps - 1) * D * 2),
+                   C.c_uint64(steps * D * 2), C.c_uint64(D * 2), C.c_uint64(B))
+            N.call("ns_layernorm", h, C.c_uint64(self.last.ptr), N.NS_BF16, self.lnf[0].ptr, self.lnf[1].ptr, C.c_int64(B), D, eps, N.NS_I8, hq, hs)
+            self._n += 2
+        self.head.forward(hq, hs, B, N.EPI_BIAS, N.NS_F32, self.logits.ptr)
+        if self.tp == 1:
+            N.call("ns_argmax_i32", h, self.logits.ptr, B, cfg.vocab, C.c_int64(cfg.vocab), self.ids.ptr)
+            self._n += 2
+        else:
+            N.call("ns_argmax_partial", h, self.logits.ptr, B, self.v_loc, C.c_int64(self.v_loc), self.rank * self.v_loc, self.am_val.ptr, self.am_idx.ptr)
+            N.call("ns_allgather", h, self.comm, C.c_uint64(self.am_val.ptr), C.c_uint64(self.am_vals.ptr), C.c_int64(B), N.NS_F32)
+            N.call("ns_allgather", h, self.comm, C.c_uint64(self.am_idx.ptr), C.c_uint64(self.am_idxs.ptr), C.c_int64(B), N.NS_I32)
+            N.call("ns_argmax_merge", h, self.am_vals.ptr, self.am_idxs.ptr, self.tp, B, self.ids.ptr)
+            self._n += 5
+        N.call("ns_add_i32", h, self.pos.ptr, steps)
+        self._n += 1
+        self.x = [x_in, x_out]
+
+    def _attention_splits(self, steps: int) -> int:
+        """How many ways ns_attention_decode splits the cache for this pass (a combine kernel follows when > 1): the rule of
+        the library (rows under two CTAs per SM are split, each part at least 256 positions, at most 32 parts)."""
+        rows = self.batch * self.heads_loc * steps
+        target = 2 * self.dev.sm_count
+        if rows >= target:
+            return 1
+        return max(1, min((target + rows - 1) // rows, max(1, (self.max_pages * self.page_size) // 256), 32))
 
     def _forward_tp_fused(self, steps: int) -> None:
         """The few-row pass on several GPUs: as _forward_fused, but a row-parallel product (attention output, FF2) writes

@@ -76,6 +76,11 @@ SIGNATURES = {
     "ns_linear_forward_partial": [vp, vp, u64, i32, P(u64), P(i32)],
     "ns_finish_norm_quant": [vp, u64, i32, vp, u64, u64, i64, u64, u64, u64, f32, u64, u64],
     "ns_finish_kv_append": [vp, u64, i32, vp, u64, i32, i32, u64, vp, u64, i32, u64],
+    "ns_linear_forward_norm_quant": [vp, vp, u64, u64, u64, i64, u64, u64, u64, f32, u64, u64],
+    "ns_linear_forward_gelu_quant": [vp, vp, u64, u64, i64, u64, u64],
+    "ns_linear_forward_kv_append": [vp, vp, u64, u64, i32, i32, u64, vp, u64, i32, u64],
+    "ns_linear_forward_tp_norm_quant": [vp, vp, vp, i32, u64, u64, u64, i64, u64, u64, u64, f32, u64, u64],
+    "ns_attention_decode_quant": [vp, vp, u64, i64, u64, i64, u64, i32, u64, i32, i32, f32, u64, u64],
     "ns_bias_residual": [vp, u64, u64, u64, i32, i64, i32, i32, u64],
     "ns_argmax_partial": [vp, u64, i32, i32, i64, i32, u64, u64],
     "ns_argmax_merge": [vp, u64, u64, i32, i32, u64],
