@@ -191,7 +191,8 @@ def decode_step_bytes(cfg, batch: int, context: float, gpus: int) -> float:
     return (weights + kv) / gpus
 
 
-def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tokens: int, compare_tp1: bool):
+def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tokens: int, compare_tp1: bool, fused: int | None = None,
+                   attn_quant: bool | None = None):
     """Builds the decoder tensor-parallel over the ranks of the run, warms up, times one generation; returns the
     `gpt_decode` record on rank 0 (None elsewhere)."""
     from nn_b200 import dist as nsdist
@@ -207,6 +208,10 @@ def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tok
         comm, _, _ = nsdist.init_comm(dev)
     t0 = time.perf_counter()
     model = GptW8A8(dev, cfg, weights, B, max_prefill=P, tp_rank=rank, tp_size=world, comm=comm)
+    if fused is not None:
+        model.fused = fused
+    if attn_quant is not None:
+        model.attn_quant = attn_quant
     build_s = time.perf_counter() - t0
 
     model.generate(prompt, min(g["warmup_tokens"], new_tokens))       # warm-up generation: sizes scratch, records the step graph
@@ -543,10 +548,12 @@ def run_case(spec: str):
                               prints the TOPS of 200 timed launches -- the int8 tensor-core rate the load / MMA pipeline reaches
       attention_decode:L      batch 64, 32 heads, head_dim 128, cache length L
       attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
-      gpt_decode:LAYERS[:T]   the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64,
+      gpt_decode:LAYERS[:T[:F[:Q]]] the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64,
                               prompt 512) cut to LAYERS layers, T new tokens (default 64): prints the gpt_decode record
                               of the default run.  Under `python -m torch.distributed.run --nproc-per-node N` the decoder
-                              is tensor-parallel over N GPUs (one rank per GPU, the slowest rank's times are printed by rank 0)
+                              is tensor-parallel over N GPUs (one rank per GPU, the slowest rank's times are printed by rank 0).
+                              F picks the few-row pass: 2 one launch per Linear, 1 product + fused row kernel, 0 one kernel per operator;
+                              Q = 0 keeps the row quantisation after attention a kernel of its own
     """
     from nn_b200 import native as N
     from nn_b200.device import Device
@@ -617,9 +624,10 @@ def run_case(spec: str):
             N.call("ns_attention_prefill", dev.handle, q.ptr, k.ptr, v.ptr, o.ptr, B, H, S, 128, st, st, st, st, C.c_float(0.0884), 1)
     elif name == "gpt_decode":
         from nn_b200 import dist as nsdist
-        layers, _, toks = arg.partition(":")
+        parts = arg.split(":") + ["", "", "", ""]
         rank, world, _ = nsdist.env_rank()
-        rec = run_gpt_decode(dev, rank, world, measured_peaks(), int(layers or 2), int(toks or 64), compare_tp1=False)
+        rec = run_gpt_decode(dev, rank, world, measured_peaks(), int(parts[0] or 2), int(parts[1] or 64), compare_tp1=False,
+                             fused=int(parts[2]) if parts[2] else None, attn_quant=bool(int(parts[3])) if parts[3] else None)
         if rank == 0:
             print(json.dumps({"case": spec, "ok": True, "gpt_decode": rec}))
         return

@@ -81,6 +81,10 @@ NS_API int ns_device_status(ns_device_t dev, int* status);
  * every kernel variant on one shape.  tile_n: 0 = heuristic, 64 / 128 / 256 = that tile width with the single-CTA
  * kernel, NS_TUNE_NARROW = the narrowest tile, NS_TUNE_PAIR = the CTA-pair kernel wherever a shape allows it.
  * k_splits: 0 = heuristic, otherwise the split-K count.  A host binding has no reason to import this. */
+/* TEST HOOK, not for hosts: while `buffer` (device memory, 4 x 8 bytes per SM) is non-zero, every CTA of a product with a
+ * second phase (ns_linear_forward_norm_quant and its siblings) records four times in nanoseconds there: kernel start,
+ * product done, all CTAs arrived, rows done.  0 turns it off. */
+NS_API int ns_debug_tail_times(ns_device_t dev, uint64_t buffer);
 #define NS_TUNE_NARROW 32
 #define NS_TUNE_PAIR 512
 NS_API int ns_device_tune(ns_device_t dev, int tile_n, int k_splits);

@@ -59,6 +59,7 @@ struct NsDevice {
     std::vector<void*> retired_scratch;
     // words for grid-wide phases inside one kernel (arrival counters, per-row tickets); zero between kernels
     uint32_t* sync_words = nullptr;
+    unsigned long long* tail_times = nullptr;   // test hook (ns_debug_tail_times)
     // tuning overrides (0 = heuristic)
     int force_bn = 0;
     int force_splits = 0;

@@ -507,6 +507,7 @@ __global__ void __launch_bounds__(NS_TAIL_THREADS, 1)
 ns_gemm_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ StoreMaps sm, const NsGemmParams p, const __grid_constant__ NsTail tail)
 {
+    ns_tail::stamp(tail, 0);
     gemm_tc_body<NS_KIND_I8, BN, false, true>(tmA, tmB, sm, p);
     ns_tail::run(tail);
 }
@@ -1049,6 +1050,7 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
         }
         tail->sync = d->sync_words;
         tail->status = d->status_dev;
+        tail->times = d->tail_times;
         switch (bn) {
             case 256: return launch_gemm_tail<256>(d, tmA, tmB, sm, p, *tail);
             case 128: return launch_gemm_tail<128>(d, tmA, tmB, sm, p, *tail);

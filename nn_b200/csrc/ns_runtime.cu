@@ -193,6 +193,14 @@ extern "C" int ns_device_tune(ns_device_t h, int tile_n, int k_splits)
     return NS_OK;
 }
 
+extern "C" int ns_debug_tail_times(ns_device_t h, uint64_t buffer)
+{
+    NsDevice* d = ns_dev(h);
+    NS_REQUIRE(d != nullptr, NS_ERR_ARGUMENT, "ns_debug_tail_times: device is null");
+    d->tail_times = reinterpret_cast<unsigned long long*>(buffer);
+    return NS_OK;
+}
+
 int ns_scratch_reserve(NsDevice* d, size_t bytes, void** out)
 {
     if (bytes > d->scratch_bytes) {

@@ -60,12 +60,23 @@ struct NsTail {
     const uint32_t* local_flags;
     uint32_t* epoch;
     int rank, world;
+    // test hook: when non-null, CTA b writes the time (ns) of four points of its second phase to times[4 b ..]
+    unsigned long long* times;
 };
 
 // The device code is compiled into the one source file that defines NS_TAIL_DEVICE_CODE before including this header
 // (ns_gemm_tc.cu); the others only need the struct.
 #if defined(__CUDACC__) && defined(NS_TAIL_DEVICE_CODE)
 namespace ns_tail {
+
+__device__ __forceinline__ void stamp(const NsTail& t, int slot)
+{
+    if (t.times != nullptr && threadIdx.x == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        t.times[4 * blockIdx.x + slot] = now;
+    }
+}
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p)
 {
@@ -459,7 +470,9 @@ __device__ __noinline__ void run(const NsTail& t)
     const bool all_wait = t.kind == NS_TAIL_KV;
     const bool waits = all_wait || (int64_t)blockIdx.x < t.rows;
     const unsigned waiters = all_wait ? gridDim.x : (unsigned)(t.rows < (int64_t)gridDim.x ? t.rows : (int64_t)gridDim.x);
+    stamp(t, 1);
     const bool ok = arrive_and_wait(t.sync, waits, t.status, 420 + t.kind, &flag);
+    stamp(t, 2);
     if (!waits) return;
     if (ok) {
         if (t.kind == NS_TAIL_KV) {
@@ -478,6 +491,7 @@ __device__ __noinline__ void run(const NsTail& t)
             }
         }
     }
+    stamp(t, 3);
     depart(t.sync, waiters);
 }
 

@@ -151,9 +151,11 @@ class GptW8A8:
             self.am_val, self.am_idx = dev.empty(batch), dev.empty(batch, N.NS_I32)
             self.am_vals, self.am_idxs = dev.empty(batch * tp_size), dev.empty(batch * tp_size, N.NS_I32)
         self.length = 0          # host mirror of the device position (DecodingContext.Length, Layers/Decoding.cs:75)
-        # few-row passes: 2 = one launch per Linear (the row operator that follows runs as the product kernel's second phase),
-        # 1 = product kernel + fused row kernel, 0 / False = one kernel per operator
-        self.fused = 2
+        # few-row passes: 1 = product kernel + fused row kernel (the default: fastest, the next product's weight fetch
+        # overlaps the row kernel), 2 = one launch per Linear (the row operator runs as the product kernel's second phase;
+        # fewer launches, measured slower), 0 / False = one kernel per operator
+        self.fused = 1
+        self.attn_quant = True   # decode attention quantises its output rows itself (one launch less per layer)
         self.graph = None
         self.launches_per_step = 0
 
@@ -236,6 +238,18 @@ class GptW8A8:
         self._n += 1
         self.x = [x_in, x_out]
 
+    def _attention_rows(self, cache, B: int, steps: int, scale) -> None:
+        """Cached attention of the new positions, output rows quantised for the output projection (hq, hq_scale)."""
+        h, dl, m = self.dev.handle, self.d_loc, B * steps
+        if self.attn_quant and m <= 4000:
+            N.call("ns_attention_decode_quant", h, cache, C.c_uint64(self.qkv.ptr), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
+                   self.max_pages, self.pos.ptr, B, steps, scale, self.hq.ptr, self.hq_scale.ptr)
+            self._n -= 1
+        else:
+            N.call("ns_attention_decode", h, cache, C.c_uint64(self.qkv.ptr), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
+                   self.max_pages, self.pos.ptr, B, steps, scale)
+            N.call("ns_quantize_rows_i8", h, self.attn.ptr, N.NS_BF16, C.c_int64(m), dl, self.hq.ptr, self.hq_scale.ptr)
+
     def _forward_fused(self, steps: int) -> None:
         """The same pass for few rows (a decoding step) with the products' epilogues moved into the row kernels that
         follow them: per layer QKV product, dequantise + bias + KV append, attention, quantise, out product, dequantise +
@@ -256,10 +270,7 @@ class GptW8A8:
             part, sp = L["qkv"].forward_partial(self.hq.ptr, m)
             N.call("ns_finish_kv_append", h, C.c_uint64(part), sp, L["qkv"].handle, self.hq_scale.ptr, B, steps, self.qkv.ptr, cache,
                    self.page_table.ptr, self.max_pages, self.pos.ptr)
-            q = self.qkv.ptr
-            N.call("ns_attention_decode", h, cache, C.c_uint64(q), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
-                   self.max_pages, self.pos.ptr, B, steps, scale)
-            N.call("ns_quantize_rows_i8", h, self.attn.ptr, N.NS_BF16, C.c_int64(m), dl, self.hq.ptr, self.hq_scale.ptr)
+            self._attention_rows(cache, B, steps, scale)
             part, sp = L["out"].forward_partial(self.hq.ptr, m)
             N.call("ns_finish_norm_quant", h, C.c_uint64(part), sp, L["out"].handle, self.hq_scale.ptr, x_in.ptr, C.c_int64(m), x_out.ptr,
                    L["ln2"][0].ptr, L["ln2"][1].ptr, eps, self.hq.ptr, self.hq_scale.ptr)
@@ -398,9 +409,7 @@ class GptW8A8:
             part, sp = L["qkv"].forward_partial(self.hq.ptr, m)
             N.call("ns_finish_kv_append", h, C.c_uint64(part), sp, L["qkv"].handle, self.hq_scale.ptr, B, steps, self.qkv.ptr, cache,
                    self.page_table.ptr, self.max_pages, self.pos.ptr)
-            N.call("ns_attention_decode", h, cache, C.c_uint64(self.qkv.ptr), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
-                   self.max_pages, self.pos.ptr, B, steps, scale)
-            N.call("ns_quantize_rows_i8", h, self.attn.ptr, N.NS_BF16, C.c_int64(m), dl, self.hq.ptr, self.hq_scale.ptr)
+            self._attention_rows(cache, B, steps, scale)
             L["out"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_NONE, N.NS_F32, self.peer_slots[0])
             N.call("ns_tp_reduce_norm_quant", h, self.peer, 0, C.c_uint64(L["out"].bias_ptr), x_in.ptr, C.c_int64(m), D, x_out.ptr,
                    L["ln2"][0].ptr, L["ln2"][1].ptr, eps, self.hq.ptr, self.hq_scale.ptr)

@@ -30,6 +30,7 @@ SIGNATURES = {
     "ns_stream_sync": [vp],
     "ns_device_status": [vp, P(i32)],
     "ns_device_tune": [vp, i32, i32],
+    "ns_debug_tail_times": [vp, u64],
     "ns_alloc": [vp, u64, i32, P(u64)],
     "ns_free": [vp, u64],
     "ns_h2d": [vp, u64, vp, u64],
