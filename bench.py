@@ -212,6 +212,9 @@ def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tok
         model.fused = fused
     if attn_quant is not None:
         model.attn_quant = attn_quant
+    if world > 1:
+        # the prompt is read by batch sharding (a full copy of the weights per GPU), decoding is tensor-parallel
+        model.enable_batch_sharded_prefill(weights)
     build_s = time.perf_counter() - t0
 
     model.generate(prompt, min(g["warmup_tokens"], new_tokens))       # warm-up generation: sizes scratch, records the step graph
@@ -259,6 +262,27 @@ def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tok
         model.set_local_exchange(False)
         exchange = {"ms_per_step_full": full, "ms_per_step_single_rank_exchange": local, "exchange_ms_per_step": full - local,
                     "context": f"{P}+3..{P}+51"}
+    # the alternative partition: pure batch sharding -- every GPU decodes batch / N sequences with the full weights, no
+    # exchange at all (the one-GPU model each rank already holds for the prompt read)
+    alt, alt_tokens = None, None
+    if world > 1 and model.replica is not None:
+        rep, bl = model.replica, B // world
+        sub = prompt[rank * bl:(rank + 1) * bl]
+        rep.generate(sub, min(g["warmup_tokens"], new_tokens))
+        dev.synchronize()
+        nsdist.barrier()
+        m2 = {}
+        toks, _ = rep.generate(sub, new_tokens, marks=m2)
+        dev.synchronize()
+        p_ms = nsdist.all_reduce_max(dev.elapsed_ms(m2["start"], m2["prefill_end"]))
+        d_ms = nsdist.all_reduce_max(dev.elapsed_ms(m2["prefill_end"], m2["steps"][-1][1]))
+        gathered = nsdist.all_gather_bytes(np.ascontiguousarray(toks, np.int32).tobytes())
+        alt_tokens = np.concatenate([np.frombuffer(x, np.int32).reshape(bl, new_tokens) for x in gathered], axis=0)
+        alt = {"parallelism": f"batch sharding: {world} x {bl} sequences, full weights per GPU, no exchange",
+               "tokens_per_s": B * n_steps / (d_ms * 1e-3), "prefill_ms": p_ms, "ms_per_step": d_ms / n_steps, "launches_per_step": rep.launches_per_step,
+               "hbm_frac": (decode_step_bytes(cfg, B, P + new_tokens / 2.0, 1) - (1.0 - 1.0 / world) * cfg.layers * 2 * B * (P + new_tokens / 2.0) * cfg.dim * 2)
+                           / (d_ms / n_steps * 1e-3) / 1e9 / peaks["hbm"]}
+    prefill_mode = "batch sharding + key/value delivery over peer memory" if model.replica is not None else "same partition as decoding"
     model.close()
     nsdist.barrier()
 
@@ -274,6 +298,10 @@ def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tok
             prefix = int(np.argmin(same)) if not same.all() else new_tokens
             compare = {"tokens_equal_tp1_prefix": prefix, "of_steps": new_tokens,
                        "sequences_equal_throughout": int(np.all(ref_tokens == tokens, axis=1).sum()), "of_sequences": B}
+            if alt_tokens is not None:
+                same_alt = np.all(ref_tokens == alt_tokens, axis=0)
+                alt["tokens_equal_tp1_prefix"] = int(np.argmin(same_alt)) if not same_alt.all() else new_tokens
+                alt["sequences_equal_throughout"] = int(np.all(ref_tokens == alt_tokens, axis=1).sum())
             if prefix < new_tokens:
                 b = int(np.argmax(ref_tokens[:, prefix] != tokens[:, prefix]))
                 one.generate(prompt, prefix + 1)                       # deterministic: ends on the step that produced token `prefix`
@@ -296,12 +324,13 @@ def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tok
                       "parallelism": f"tp{world}" if world > 1 else "1 gpu",
                       "weights": "synthetic, seeded per tensor, every layer its own values", "seed": g["seed"]},
            "tokens_per_s": B * n_steps / (decode_ms * 1e-3), "tokens_per_s_wall_incl_prefill": B * new_tokens / wall,
-           "prefill_ms": prefill_ms, "prefill_tokens_per_s": B * P / (prefill_ms * 1e-3), "decode_ms": decode_ms, "ms_per_step": ms_step,
+           "prefill_ms": prefill_ms, "prefill_mode": prefill_mode, "prefill_tokens_per_s": B * P / (prefill_ms * 1e-3), "decode_ms": decode_ms,
+           "ms_per_step": ms_step,
            "ms_per_step_first_segment": seg[0][2], "ms_per_step_last_segment": seg[-1][2],
            "segments": [{"tokens": [a, b], "ms_per_step": ms} for a, b, ms in seg],
            "launches_per_step": launches, "context_resets": resets,
            "hbm_bytes_per_step_per_gpu": step_bytes, "hbm_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm"],
-           "hbm_peak_gbs": peaks["hbm"], "clocks": clocks, "model_build_s": build_s, "exchange": exchange}
+           "hbm_peak_gbs": peaks["hbm"], "clocks": clocks, "model_build_s": build_s, "exchange": exchange, "batch_sharded_decode": alt}
     if compare is not None:
         rec.update(compare)
     return rec

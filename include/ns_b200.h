@@ -105,6 +105,13 @@ NS_API int ns_d2d_2d_async(ns_device_t dev, uint64_t dst, uint64_t dst_pitch, ui
 NS_API int ns_memset32_async(ns_device_t dev, uint64_t dst, uint32_t value, uint64_t count);
 NS_API int ns_host_alloc(uint64_t bytes, void** ptr);   /* pinned host memory */
 NS_API int ns_host_free(void* ptr);
+/* One process per GPU: a block from ns_alloc made reachable from the other processes of the machine.  The owner exports a
+ * 64-byte handle, hands it over by its own means, a peer maps it (peer access over NVLink) and unmaps it before the owner
+ * frees the block.  No counterpart in the single-process reference (its cross-device move is a host round trip,
+ * Tensor.cs:244-253). */
+NS_API int ns_ipc_handle(ns_device_t dev, uint64_t ptr, void* handle64);
+NS_API int ns_ipc_open(ns_device_t dev, const void* handle64, uint64_t* ptr);
+NS_API int ns_ipc_close(ns_device_t dev, uint64_t ptr);
 
 /* ------------------------------------------------------------------------------------------------
  * CUDA graphs.  Replaces Backend.BeginCapture/EndCapture/AbortCapture/ReplayGraph/DestroyGraph
@@ -263,7 +270,20 @@ NS_API int ns_f32_history_push(ns_device_t dev, uint64_t ids, uint64_t history, 
  * A page table (int32 [batch, max_pages], device memory, owned by the caller) maps (sequence, position / page_size)
  * to a page; the identity table gives the reference's contiguous cache. */
 NS_API int ns_kv_cache_create(ns_device_t dev, int num_pages, int page_size, int heads, int head_dim, ns_kv_cache_t* cache);
+/* The same over pools the caller allocated with ns_alloc (256-byte aligned, num_pages * heads * page_size * head_dim * 2 bytes
+ * each) and keeps: the pools of every layer can then live in one allocation that other processes map (ns_ipc_handle). */
+NS_API int ns_kv_cache_create_in(ns_device_t dev, int num_pages, int page_size, int heads, int head_dim, uint64_t k_pool, uint64_t v_pool,
+                                 ns_kv_cache_t* cache);
 NS_API int ns_kv_cache_destroy(ns_kv_cache_t cache);
+/* The exchange step between a batch-sharded prompt read and tensor-parallel decoding (several GPUs; no counterpart in the
+ * single-device reference, it serves the prompt read of CharGpt.Generate, samples/Shared/Gpt/CharGpt.cs:261-270): `src` holds
+ * all heads of this rank's n_seqs sequences (global sequence numbers seq0 ..); for each of them the first pages_used pages of
+ * every head are copied into the cache of the rank that owns the head (heads / world consecutive heads per rank):
+ * dst_k_pools / dst_v_pools are the `world` ranks' pools as mapped in this process (its own pool at its own rank),
+ * dst_table the page table the destination caches share.  Plain 16-byte stores over NVLink; queued on the stream. */
+NS_API int ns_kv_scatter_heads(ns_device_t dev, ns_kv_cache_t src, uint64_t src_table, int src_max_pages, int n_seqs, int seq0, int pages_used,
+                               const uint64_t* dst_k_pools, const uint64_t* dst_v_pools, int world, int dst_heads, int dst_num_pages,
+                               uint64_t dst_table, int dst_max_pages);
 NS_API int ns_kv_cache_pools(ns_kv_cache_t cache, uint64_t* k_pool, uint64_t* v_pool, uint64_t* bytes_each);
 
 /* cache[b, pos + i, h, :] = k/v[(b * steps + i) * src_stride + h * head_dim + :] for i < steps; pos is an int32 in

@@ -13,6 +13,7 @@
 // int32 [batch, max_pages] maps (sequence, position / page_size) to a page.  A contiguous cache is the
 // identity table.  One (page, head) slab is page_size * head_dim * 2 bytes of contiguous memory.
 #include <math.h>
+#include <string.h>
 
 #include "ns_common.cuh"
 
@@ -21,6 +22,7 @@ struct NsKvCache {
     int num_pages, page_size, heads, head_dim;
     uint16_t* k_pool;
     uint16_t* v_pool;
+    bool owns_pools;
 };
 
 namespace {
@@ -382,6 +384,7 @@ extern "C" int ns_kv_cache_create(ns_device_t h, int num_pages, int page_size, i
     NsKvCache* c = new NsKvCache();
     c->ordinal = d->ordinal;
     c->num_pages = num_pages; c->page_size = page_size; c->heads = heads; c->head_dim = head_dim;
+    c->owns_pools = true;
     const size_t bytes = (size_t)num_pages * heads * page_size * head_dim * 2;
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->k_pool), bytes);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&c->v_pool), bytes);
@@ -403,11 +406,132 @@ extern "C" int ns_kv_cache_destroy(ns_kv_cache_t ch)
     NsKvCache* c = reinterpret_cast<NsKvCache*>(ch);
     if (!c) return NS_OK;
     cudaSetDevice(c->ordinal);
-    cudaFree(c->k_pool);
-    cudaFree(c->v_pool);
+    if (c->owns_pools) {
+        cudaFree(c->k_pool);
+        cudaFree(c->v_pool);
+    }
     delete c;
     return NS_OK;
 }
+
+// A cache over pools the caller allocated (and keeps): one device allocation can then hold the pools of every layer, which
+// is what lets another process map them (ns_ipc_handle) and write prompt keys / values straight into them.
+extern "C" int ns_kv_cache_create_in(ns_device_t h, int num_pages, int page_size, int heads, int head_dim, uint64_t k_pool, uint64_t v_pool,
+                                     ns_kv_cache_t* out)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(out != nullptr && k_pool != 0 && v_pool != 0, NS_ERR_ARGUMENT, "ns_kv_cache_create_in: null argument");
+    NS_REQUIRE(num_pages > 0 && page_size > 0 && heads > 0, NS_ERR_ARGUMENT, "ns_kv_cache_create_in: bad shape");
+    NS_REQUIRE((page_size & (page_size - 1)) == 0, NS_ERR_ARGUMENT, "ns_kv_cache_create_in: page_size must be a power of two (got %d)", page_size);
+    NS_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 128, NS_ERR_ARGUMENT, "ns_kv_cache_create_in: head_dim must be 32, 64 or 128");
+    NS_REQUIRE(((k_pool | v_pool) & 255) == 0, NS_ERR_ARGUMENT, "ns_kv_cache_create_in: pools must be 256-byte aligned");
+    NsKvCache* c = new NsKvCache();
+    c->ordinal = d->ordinal;
+    c->num_pages = num_pages; c->page_size = page_size; c->heads = heads; c->head_dim = head_dim;
+    c->k_pool = reinterpret_cast<uint16_t*>(k_pool);
+    c->v_pool = reinterpret_cast<uint16_t*>(v_pool);
+    c->owns_pools = false;
+    const size_t bytes = (size_t)num_pages * heads * page_size * head_dim * 2;
+    NS_CUDA(cudaMemsetAsync(c->k_pool, 0, bytes, d->stream));
+    NS_CUDA(cudaMemsetAsync(c->v_pool, 0, bytes, d->stream));
+    *out = reinterpret_cast<ns_kv_cache_t>(c);
+    return NS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Prompt keys / values from a batch-sharded prefill into head-sharded caches.
+//
+// On several GPUs the prompt is read by batch sharding (every GPU holds a full copy of the weights and reads batch / ranks
+// sequences with no collective), while decoding is tensor-parallel: each GPU's cache holds heads / ranks heads of ALL
+// sequences.  The one exchange step in between: every GPU copies, for each of its sequences, the (page, head) slabs of
+// its full-head cache into the cache of the rank that owns the head -- plain 16-byte stores into peer-mapped memory
+// (NVLink), the local share included.  A slab (page_size x head_dim bf16) is contiguous on both sides.  The reference is
+// single-device; the caller it serves is the prompt read of CharGpt.Generate (samples/Shared/Gpt/CharGpt.cs:261-270).
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+struct KvScatterParams {
+    const uint16_t* src_k;
+    const uint16_t* src_v;
+    const int32_t* src_table;     // [n_seqs, src_max_pages]
+    int src_max_pages, src_heads;
+    uint16_t* dst_k[8];
+    uint16_t* dst_v[8];
+    const int32_t* dst_table;     // [batch, dst_max_pages], this rank's copy
+    int dst_max_pages, dst_heads, dst_num_pages;
+    int n_seqs, seq0, pages_used, world;
+    int slab_vec;                 // 16-byte vectors per slab
+    int* status;
+};
+
+__global__ void __launch_bounds__(256) ns_kv_scatter_heads_kernel(const KvScatterParams p)
+{
+    ns_pdl_wait();
+    ns_pdl_trigger();
+    const int slabs = p.n_seqs * p.pages_used * p.src_heads;
+    for (int s = blockIdx.x; s < slabs; s += gridDim.x) {
+        const int h = s % p.src_heads;
+        const int j = (s / p.src_heads) % p.pages_used;
+        const int b = s / (p.src_heads * p.pages_used);
+        const int sp = p.src_table[(size_t)b * p.src_max_pages + j];
+        const int dp = p.dst_table[(size_t)(p.seq0 + b) * p.dst_max_pages + j];
+        const int r = h / p.dst_heads, hl = h % p.dst_heads;
+        if (dp < 0 || dp >= p.dst_num_pages || r >= p.world) {
+            if (threadIdx.x == 0) *reinterpret_cast<volatile int*>(p.status) = 510;
+            continue;
+        }
+        const size_t so = ((size_t)sp * p.src_heads + h) * p.slab_vec;
+        const size_t dofs = ((size_t)dp * p.dst_heads + hl) * p.slab_vec;
+        const uint4* sk = reinterpret_cast<const uint4*>(p.src_k) + so;
+        const uint4* sv = reinterpret_cast<const uint4*>(p.src_v) + so;
+        uint4* dk = reinterpret_cast<uint4*>(p.dst_k[r]) + dofs;
+        uint4* dv = reinterpret_cast<uint4*>(p.dst_v[r]) + dofs;
+        for (int i = threadIdx.x; i < p.slab_vec; i += blockDim.x) {
+            const uint4 a = __ldg(sk + i), c = __ldg(sv + i);
+            dk[i] = a;
+            dv[i] = c;
+        }
+    }
+}
+}  // namespace
+
+extern "C" int ns_kv_scatter_heads(ns_device_t h, ns_kv_cache_t src, uint64_t src_table, int src_max_pages, int n_seqs, int seq0, int pages_used,
+                                   const uint64_t* dst_k_pools, const uint64_t* dst_v_pools, int world, int dst_heads, int dst_num_pages,
+                                   uint64_t dst_table, int dst_max_pages)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NsKvCache* c = reinterpret_cast<NsKvCache*>(src);
+    NS_REQUIRE(c && src_table && dst_table && dst_k_pools && dst_v_pools, NS_ERR_ARGUMENT, "ns_kv_scatter_heads: null argument");
+    NS_REQUIRE(world >= 1 && world <= 8 && dst_heads >= 1 && dst_heads * world == c->heads, NS_ERR_ARGUMENT,
+               "ns_kv_scatter_heads: %d ranks x %d heads do not make the source's %d heads", world, dst_heads, c->heads);
+    NS_REQUIRE(n_seqs >= 0 && seq0 >= 0 && pages_used >= 0 && pages_used <= src_max_pages && pages_used <= dst_max_pages, NS_ERR_ARGUMENT,
+               "ns_kv_scatter_heads: bad shape");
+    if (n_seqs == 0 || pages_used == 0) return NS_OK;
+    KvScatterParams p;
+    memset(&p, 0, sizeof(p));
+    p.src_k = c->k_pool; p.src_v = c->v_pool;
+    p.src_table = reinterpret_cast<const int32_t*>(src_table);
+    p.src_max_pages = src_max_pages; p.src_heads = c->heads;
+    for (int r = 0; r < world; r++) {
+        NS_REQUIRE(dst_k_pools[r] != 0 && dst_v_pools[r] != 0 && ((dst_k_pools[r] | dst_v_pools[r]) & 15) == 0, NS_ERR_ARGUMENT,
+                   "ns_kv_scatter_heads: pool of rank %d is null or misaligned", r);
+        p.dst_k[r] = reinterpret_cast<uint16_t*>(dst_k_pools[r]);
+        p.dst_v[r] = reinterpret_cast<uint16_t*>(dst_v_pools[r]);
+    }
+    p.dst_table = reinterpret_cast<const int32_t*>(dst_table);
+    p.dst_max_pages = dst_max_pages; p.dst_heads = dst_heads; p.dst_num_pages = dst_num_pages;
+    p.n_seqs = n_seqs; p.seq0 = seq0; p.pages_used = pages_used; p.world = world;
+    p.slab_vec = c->page_size * c->head_dim * 2 / 16;
+    p.status = d->status_dev;
+    const int64_t slabs = (int64_t)n_seqs * pages_used * c->heads;
+    const int64_t cap = (int64_t)d->sm_count * 8;
+    NS_CUDA(ns_launch_plain(ns_kv_scatter_heads_kernel, dim3((unsigned)(slabs < cap ? slabs : cap)), dim3(256), 0, d->stream, p));
+    return NS_OK;
+}
+
 
 extern "C" int ns_kv_cache_pools(ns_kv_cache_t ch, uint64_t* k_pool, uint64_t* v_pool, uint64_t* bytes_each)
 {

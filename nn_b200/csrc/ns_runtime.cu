@@ -347,6 +347,47 @@ extern "C" int ns_host_free(void* ptr)
 }
 
 // ------------------------------------------------------------------------------------------------
+// memory shared between the processes of one machine (one process per GPU)
+// ------------------------------------------------------------------------------------------------
+extern "C" int ns_ipc_handle(ns_device_t h, uint64_t ptr, void* handle64)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(ptr != 0 && handle64 != nullptr, NS_ERR_ARGUMENT, "ns_ipc_handle: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t ipc;
+    NS_CUDA(cudaIpcGetMemHandle(&ipc, reinterpret_cast<void*>(ptr)));
+    memcpy(handle64, &ipc, 64);
+    return NS_OK;
+}
+
+extern "C" int ns_ipc_open(ns_device_t h, const void* handle64, uint64_t* ptr)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(handle64 != nullptr && ptr != nullptr, NS_ERR_ARGUMENT, "ns_ipc_open: null argument");
+    cudaIpcMemHandle_t ipc;
+    memcpy(&ipc, handle64, 64);
+    void* p = nullptr;
+    NS_CUDA(cudaIpcOpenMemHandle(&p, ipc, cudaIpcMemLazyEnablePeerAccess));
+    *ptr = reinterpret_cast<uint64_t>(p);
+    return NS_OK;
+}
+
+extern "C" int ns_ipc_close(ns_device_t h, uint64_t ptr)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    if (ptr == 0) return NS_OK;
+    NS_CUDA(cudaStreamSynchronize(d->stream));
+    NS_CUDA(cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)));
+    return NS_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
 // graphs
 // ------------------------------------------------------------------------------------------------
 struct NsGraph {

@@ -51,6 +51,18 @@ def init_comm(dev: Device):
     return comm, rank, world
 
 
+def all_gather_bytes(payload: bytes) -> list[bytes]:
+    """Every rank's `payload` (same length everywhere), in rank order, over gloo."""
+    import torch
+    import torch.distributed as dist
+
+    if not dist.is_initialized():
+        dist.init_process_group("gloo")
+    parts = [torch.zeros(len(payload), dtype=torch.uint8) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, torch.frombuffer(bytearray(payload), dtype=torch.uint8).clone())
+    return [bytes(t.numpy().tobytes()) for t in parts]
+
+
 def make_peer_group(dev: Device, rank: int, world: int, slot_bytes: int):
     """A peer-memory group for ns_tp_reduce_norm_quant: every rank's 64-byte IPC handle is gathered over gloo."""
     import torch

@@ -117,11 +117,18 @@ class GptW8A8:
         self.page_size = page_size
         self.max_pages = (cfg.context + page_size - 1) // page_size
         self.page_table = dev.from_numpy(np.arange(batch * self.max_pages, dtype=np.int32))
+        # the pools of every layer in ONE allocation (keys of layer 0, values of layer 0, keys of layer 1, ...), so that the
+        # other ranks of a tensor-parallel run can map them and deliver prompt keys / values (batch-sharded prefill)
+        self.pool_bytes = batch * self.max_pages * self.heads_loc * page_size * cfg.head_dim * 2
+        self.kv_block = dev.empty(2 * cfg.layers * self.pool_bytes, N.NS_I8)
         self.caches = []
-        for _ in range(cfg.layers):
+        for i in range(cfg.layers):
             h = C.c_void_p()
-            N.call("ns_kv_cache_create", dev.handle, batch * self.max_pages, page_size, self.heads_loc, cfg.head_dim, C.byref(h))
+            N.call("ns_kv_cache_create_in", dev.handle, batch * self.max_pages, page_size, self.heads_loc, cfg.head_dim,
+                   C.c_uint64(self.kv_block.ptr + 2 * i * self.pool_bytes), C.c_uint64(self.kv_block.ptr + (2 * i + 1) * self.pool_bytes), C.byref(h))
             self.caches.append(h)
+        self.replica = None            # a one-GPU model of batch / tp sequences for the batch-sharded prompt read
+        self._peer_kv = None           # every rank's kv_block as mapped here
         # activations (sized for the longest prefill) and device-side state
         R = self.max_rows
         self.x = [dev.empty(R * D, N.NS_BF16), dev.empty(R * D, N.NS_BF16)]
@@ -448,11 +455,56 @@ class GptW8A8:
         N.call("ns_memset32_async", self.dev.handle, C.c_uint64(self.pos.ptr), 0, C.c_uint64(1))
         self.length = 0
 
+    def enable_batch_sharded_prefill(self, weights: dict) -> None:
+        """Several GPUs: from now on the prompt is read by BATCH sharding -- this rank reads batch / tp sequences with a full
+        copy of the weights and no collective (the read is compute-bound and scales with the GPUs), then delivers the keys
+        and values of its sequences to the ranks that own the heads (ns_kv_scatter_heads: stores into the peers' caches
+        over NVLink), and the first tokens are gathered.  Decoding stays tensor-parallel.  Costs a second copy of the int8
+        weights (unsharded) and a cache for batch / tp sequences on every GPU."""
+        if self.tp == 1 or self.replica is not None:
+            return
+        assert self.batch % self.tp == 0, "the batch must divide over the ranks"
+        from . import dist
+        self.replica = GptW8A8(self.dev, self.cfg, weights, self.batch // self.tp, self.max_rows // self.batch, page_size=self.page_size)
+        mine = C.create_string_buffer(64)
+        N.call("ns_ipc_handle", self.dev.handle, C.c_uint64(self.kv_block.ptr), mine)
+        self._peer_kv = []
+        for r, handle in enumerate(dist.all_gather_bytes(mine.raw)):
+            if r == self.rank:
+                self._peer_kv.append(self.kv_block.ptr)
+            else:
+                ptr = C.c_uint64()
+                N.call("ns_ipc_open", self.dev.handle, handle, C.byref(ptr))
+                self._peer_kv.append(ptr.value)
+
+    def _prefill_batch_sharded(self, ids: np.ndarray) -> None:
+        from . import dist
+        rep, bl, t = self.replica, self.batch // self.tp, ids.shape[1]
+        h = self.dev.handle
+        # every rank must be done with its previous step (it reads its cache) before a peer overwrites that cache
+        self.dev.synchronize()
+        dist.barrier()
+        rep.prefill(ids[self.rank * bl:(self.rank + 1) * bl])
+        pages_used = (t + self.page_size - 1) // self.page_size
+        arr = C.c_uint64 * self.tp
+        for i, cache in enumerate(rep.caches):
+            dk = arr(*[p + 2 * i * self.pool_bytes for p in self._peer_kv])
+            dv = arr(*[p + (2 * i + 1) * self.pool_bytes for p in self._peer_kv])
+            N.call("ns_kv_scatter_heads", h, cache, rep.page_table.ptr, rep.max_pages, bl, self.rank * bl, pages_used, dk, dv, self.tp, self.heads_loc,
+                   self.batch * self.max_pages, self.page_table.ptr, self.max_pages)
+        # the first tokens of all sequences; a rank's share leaves only after its stores above are complete (stream order), and
+        # the gather completes only when every rank has contributed: after it, every cache holds every sequence's prompt
+        N.call("ns_allgather", h, self.comm, C.c_uint64(rep.ids.ptr), C.c_uint64(self.ids.ptr), C.c_int64(bl), N.NS_I32)
+        N.call("ns_memset32_async", h, C.c_uint64(self.pos.ptr), t, C.c_uint64(1))
+        self.length = t
+
     def prefill(self, ids: np.ndarray) -> None:
         """ids [batch, t]: reads t positions from position 0 and samples the next token into ids[0:batch]."""
         ids = np.ascontiguousarray(ids, dtype=np.int32)
         b, t = ids.shape
         assert b == self.batch
+        if self.replica is not None:
+            return self._prefill_batch_sharded(ids)
         self.reset()
         N.call("ns_h2d", self.dev.handle, C.c_uint64(self.ids.ptr), ids.ctypes.data_as(C.c_void_p), C.c_uint64(ids.nbytes))
         self._forward(t)
@@ -583,9 +635,22 @@ class GptW8A8:
             if self._peer_solo is not None:
                 N.call("ns_peer_group_destroy", self._peer_solo[0])
             self.peer = self._peer_all = self._peer_solo = None
+        if self._peer_kv is not None:
+            from . import dist
+            self.dev.synchronize()
+            dist.barrier()             # no peer may still be storing into this rank's cache, nor this rank into a peer's
+            for r, ptr in enumerate(self._peer_kv):
+                if r != self.rank:
+                    N.call("ns_ipc_close", self.dev.handle, C.c_uint64(ptr))
+            self._peer_kv = None
+            dist.barrier()
+        if self.replica is not None:
+            self.replica.close()
+            self.replica = None
         for c in self.caches:
             N.call("ns_kv_cache_destroy", c)
         self.caches = []
+        self.kv_block.release()
         for L in self.layers:
             for k in ("qkv", "out", "ff1", "ff2"):
                 L[k].close()

@@ -42,6 +42,9 @@ SIGNATURES = {
     "ns_memset32_async": [vp, u64, u32, u64],
     "ns_host_alloc": [u64, P(vp)],
     "ns_host_free": [vp],
+    "ns_ipc_handle": [vp, u64, vp],
+    "ns_ipc_open": [vp, vp, P(u64)],
+    "ns_ipc_close": [vp, u64],
     "ns_capture_begin": [vp],
     "ns_capture_end": [vp, P(vp)],
     "ns_capture_abort": [vp],
@@ -64,7 +67,9 @@ SIGNATURES = {
     "ns_fill_normal": [vp, u64, i32, i64, u32, f32, f32],
     "ns_fill_ids": [vp, u64, i64, u32, u32],
     "ns_kv_cache_create": [vp, i32, i32, i32, i32, P(vp)],
+    "ns_kv_cache_create_in": [vp, i32, i32, i32, i32, u64, u64, P(vp)],
     "ns_kv_cache_destroy": [vp],
+    "ns_kv_scatter_heads": [vp, vp, u64, i32, i32, i32, i32, P(u64), P(u64), i32, i32, i32, u64, i32],
     "ns_kv_cache_pools": [vp, P(u64), P(u64), P(u64)],
     "ns_kv_append": [vp, vp, u64, u64, i64, u64, i32, u64, i32, i32],
     "ns_attention_decode": [vp, vp, u64, i64, u64, i64, u64, i32, u64, i32, i32, f32],
