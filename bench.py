@@ -217,7 +217,7 @@ def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tok
         model.enable_batch_sharded_prefill(weights)
     build_s = time.perf_counter() - t0
 
-    model.generate(prompt, min(g["warmup_tokens"], new_tokens))       # warm-up generation: sizes scratch, records the step graph
+    warm_tokens, _ = model.generate(prompt, min(g["warmup_tokens"], new_tokens))   # warm-up generation: sizes scratch, records the step graph
     dev.synchronize()
     nsdist.barrier()
     sampler = ClockSampler(dev.ordinal, "_gpt")
@@ -330,7 +330,8 @@ def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tok
            "segments": [{"tokens": [a, b], "ms_per_step": ms} for a, b, ms in seg],
            "launches_per_step": launches, "context_resets": resets,
            "hbm_bytes_per_step_per_gpu": step_bytes, "hbm_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm"],
-           "hbm_peak_gbs": peaks["hbm"], "clocks": clocks, "model_build_s": build_s, "exchange": exchange, "batch_sharded_decode": alt}
+           "hbm_peak_gbs": peaks["hbm"], "clocks": clocks, "model_build_s": build_s, "exchange": exchange, "batch_sharded_decode": alt,
+           "tokens_equal_on_repeat": bool(np.array_equal(warm_tokens, tokens[:, :warm_tokens.shape[1]]))}
     if compare is not None:
         rec.update(compare)
     return rec

@@ -430,9 +430,15 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
                 const float m_all = fmaxf(m_ref, m_o);
                 const float a_mine = m_ref == -INFINITY ? 0.0f : fa_exp2((m_ref - m_all) * p.scale_log2);
                 const float a_other = m_o == -INFINITY ? 0.0f : fa_exp2((m_o - m_all) * p.scale_log2);
-                const float l_tot = l_run * a_mine + l_o * a_other;
+                // Which group got the tile's even-numbered key blocks depends on how many blocks this CTA has walked before
+                // (tiles are drawn from a counter at run time).  The result must not: the two partial results are combined
+                // in the order (even blocks, odd blocks) of the TILE, whichever group holds which, with every rounding spelt out.
+                const bool mine_even = ((g - gj0) & 1) == 0;
+                const float l_even = mine_even ? l_run : l_o, a_even = mine_even ? a_mine : a_other;
+                const float l_odd = mine_even ? l_o : l_run, a_odd = mine_even ? a_other : a_mine;
+                const float l_tot = __fadd_rn(__fmul_rn(l_even, a_even), __fmul_rn(l_odd, a_odd));
                 const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
-                const float w_mine = a_mine * inv, w_other = a_other * inv;
+                const float w_even = __fmul_rn(a_even, inv), w_odd = __fmul_rn(a_odd, inv);
                 const uint32_t o_mine = lane_addr + 256 + g * 128, o_other = lane_addr + 256 + (g ^ 1) * 128;
                 // group g finishes output dims [64 g, 64 g + 64): (O_mine w_mine + O_other w_other) -> bf16 -> the upper half of
                 // its P buffer -> one TMA store per warp.  An accumulator that was not written in this tile (a group without
@@ -452,8 +458,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1) ns_attention_prefill_kernel(con
 #pragma unroll
                     for (int q = 0; q < 16; q++) {
                         // a written accumulator row is finite (a row without live keys in a group's blocks is a sum of zeros)
-                        const float x0 = fmaf(__uint_as_float(ob[2 * q]), w_other, __uint_as_float(oa[2 * q]) * w_mine);
-                        const float x1 = fmaf(__uint_as_float(ob[2 * q + 1]), w_other, __uint_as_float(oa[2 * q + 1]) * w_mine);
+                        const float e0 = __uint_as_float(mine_even ? oa[2 * q] : ob[2 * q]), d0 = __uint_as_float(mine_even ? ob[2 * q] : oa[2 * q]);
+                        const float e1 = __uint_as_float(mine_even ? oa[2 * q + 1] : ob[2 * q + 1]), d1 = __uint_as_float(mine_even ? ob[2 * q + 1] : oa[2 * q + 1]);
+                        const float x0 = fmaf(d0, w_odd, __fmul_rn(e0, w_even));
+                        const float x1 = fmaf(d1, w_odd, __fmul_rn(e1, w_even));
                         w[q] = fa_pack_bf16(x0, x1);
                     }
 #pragma unroll

@@ -103,3 +103,25 @@ def test_baseline_shapes(dev, orc, S):
     o0 = do.download((B * H, S * DH))[:, :DH]
     v0 = dv.download((B * H, S * DH))[:, :DH]
     assert np.array_equal(o0, v0)
+
+
+def test_results_do_not_depend_on_the_tile_schedule(dev, orc):
+    """The kernel's CTAs draw their (batch, head, query tile) work from a counter at run time, so which CTA -- and which of
+    its two softmax groups -- handles a tile's even and odd key blocks changes from run to run.  The output must not:
+    three runs on the same inputs are bit-identical (a greedy decoder downstream turns a last-bit difference into
+    another token at a near-tie)."""
+    import ctypes as C
+    B, H, S = 16, 16, 640
+    n = B * H * S * 128
+    q, k, v = (dev.empty(n, N.NS_BF16) for _ in range(3))
+    for t, seed in ((q, 11), (k, 12), (v, 13)):
+        N.call("ns_fill_normal", dev.handle, t.ptr, N.NS_BF16, C.c_int64(n), seed, C.c_float(0.0), C.c_float(1.0))
+    st = (C.c_int64 * 3)(H * S * 128, S * 128, 128)
+    outs = []
+    for rep in range(3):
+        o = dev.zeros(n, N.NS_BF16)
+        N.call("ns_attention_prefill", dev.handle, q.ptr, k.ptr, v.ptr, o.ptr, B, H, S, 128, st, st, st, st, C.c_float(0.0884), 1)
+        dev.synchronize()
+        outs.append(o.download())
+        o.release()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
