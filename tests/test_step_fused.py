@@ -117,11 +117,11 @@ def test_finish_kv_append_equals_unfused(dev, orc, B, steps, heads, dh, pos0):
     N.call("ns_linear_destroy", lin)
 
 
-@pytest.mark.parametrize("dim,heads,ff", [(256, 4, 1024), (768, 6, 1536)])
+@pytest.mark.parametrize("dim,heads,ff", [(256, 4, 1024), (768, 12, 1536)])
 def test_fused_and_unfused_decoder_agree(dev, orc, dim, heads, ff):
     """The int8 decoder with one launch per Linear (2), with the fused row kernels (1) and with one kernel per operator
-    (0): same tokens, bit-identical logits (head_dim 64 / 128; the few prompt rows go through the decode attention
-    kernel in the first shape)."""
+    (0): same tokens, bit-identical logits (head_dim 64, so every variant reads the few prompt rows with the decode
+    attention kernel; with head_dim 128 the unfused variant would take the flash kernel, which rounds P to bf16)."""
     from nn_b200.gpt import GptConfig, GptW8A8
     from oracle import model as om
     cfg = GptConfig(vocab=320, dim=dim, heads=heads, layers=3, ff_dim=ff, context=48)
