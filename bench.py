@@ -192,14 +192,14 @@ def decode_step_bytes(cfg, batch: int, context: float, gpus: int) -> float:
 
 
 def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tokens: int, compare_tp1: bool, fused: int | None = None,
-                   attn_quant: bool | None = None):
+                   attn_quant: bool | None = None, batch: int | None = None):
     """Builds the decoder tensor-parallel over the ranks of the run, warms up, times one generation; returns the
     `gpt_decode` record on rank 0 (None elsewhere)."""
     from nn_b200 import dist as nsdist
     from nn_b200.gpt import GptConfig, GptW8A8
 
     g = GPT
-    B, P = g["batch"], g["prompt"]
+    B, P = batch or g["batch"], g["prompt"]
     cfg = GptConfig(vocab=g["vocab"], dim=g["dim"], heads=g["heads"], layers=layers, ff_dim=g["ff_dim"], context=P + g["new_tokens"])
     weights = SyntheticGptWeights(cfg, g["seed"])
     prompt = gpt_prompt(cfg, B, P, g["seed"])
@@ -576,14 +576,19 @@ def run_case(spec: str):
       qmatmul_i8_rows:M       int8 product of M <= 8 rows with 32768 x 8192 weights (268 MB, beyond L2): the row-streaming kernel
       i8_mainloop_peak[:K]    the pair kernel's main loop alone (ns_bench_i8_mainloop), M = 8192, N = 4096, K = 16384 unless given:
                               prints the TOPS of 200 timed launches -- the int8 tensor-core rate the load / MMA pipeline reaches
+      second_phase_times      ns_linear_forward_norm_quant / _gelu_quant at 64 rows: per-CTA times of the kernel's phases (product done,
+                              all CTAs arrived, rows done) from the library's timing hook, and the time per call
+      decode_shapes           the weight-streaming products (int8 M in {1, 16, 128} at K = N = 4096; bf16 M = 8, K = 4096, N = 14336;
+                              the five M = 64 products of the decoder step) timed as graphs of 20 launches over weight copies
+                              beyond L2, beside the same graph of an empty kernel: prints time, GB/s and fraction of the HBM peak
       attention_decode:L      batch 64, 32 heads, head_dim 128, cache length L
       attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
-      gpt_decode:LAYERS[:T[:F[:Q]]] the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64,
+      gpt_decode:LAYERS[:T[:F[:Q[:B]]]] the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64,
                               prompt 512) cut to LAYERS layers, T new tokens (default 64): prints the gpt_decode record
                               of the default run.  Under `python -m torch.distributed.run --nproc-per-node N` the decoder
                               is tensor-parallel over N GPUs (one rank per GPU, the slowest rank's times are printed by rank 0).
                               F picks the few-row pass: 2 one launch per Linear, 1 product + fused row kernel, 0 one kernel per operator;
-                              Q = 0 keeps the row quantisation after attention a kernel of its own
+                              Q = 0 keeps the row quantisation after attention a kernel of its own; B = batch instead of 64
     """
     from nn_b200 import native as N
     from nn_b200.device import Device
@@ -627,6 +632,127 @@ def run_case(spec: str):
         us = dev.elapsed_ms(e0, e1) / 200 * 1e3
         print(json.dumps({"case": spec, "ok": True, "us_per_launch": us, "tops": 2.0 * M * kp * NN / (us * 1e-6) / 1e12, "M": M, "N": NN, "K": kp}))
         return
+    elif name == "second_phase_times":
+        # One launch per Linear (ns_linear_forward_norm_quant / _gelu_quant): where the time of the product kernel's second phase
+        # goes.  Every CTA records four times (test hook ns_debug_tail_times): kernel start, product done (its stores
+        # complete), every CTA arrived, rows done.  Weights stay the same from call to call (L2-resident).
+        rng = np.random.default_rng(6)
+        rows_m = 64
+        times = dev.zeros(148 * 4 * 2, N.NS_I32)
+        out = []
+        for (k_, n_, kind) in [(2048, 2048, "norm"), (8192, 2048, "norm"), (2048, 8192, "gelu")]:
+            w = rng.standard_normal((k_, n_), dtype=np.float32) * 0.05
+            bvec = rng.standard_normal(n_, dtype=np.float32) * 0.1
+            lin = C.c_void_p()
+            N.call("ns_linear_create", dev.handle, k_, n_, N.NS_I8, w.ctypes.data_as(C.POINTER(C.c_float)), bvec.ctypes.data_as(C.POINTER(C.c_float)),
+                   N.SPLIT_NONE, 1, 0, 1, C.byref(lin))
+            x = dev.from_numpy(rng.standard_normal((rows_m, k_), dtype=np.float32))
+            xq, xs = dev.empty(rows_m * k_, N.NS_I8), dev.empty(rows_m)
+            N.call("ns_quantize_rows_i8", dev.handle, x.ptr, N.NS_F32, C.c_int64(rows_m), k_, xq.ptr, xs.ptr)
+            res = dev.empty(rows_m * n_, N.NS_BF16)
+            N.call("ns_fill_normal", dev.handle, res.ptr, N.NS_BF16, C.c_int64(rows_m * n_), 8, 0.0, 1.0)
+            gam, bet = dev.from_numpy(np.ones(n_, np.float32)), dev.from_numpy(np.zeros(n_, np.float32))
+            y, q, sc = dev.empty(rows_m * n_, N.NS_BF16), dev.empty(rows_m * max(n_, k_), N.NS_I8), dev.empty(rows_m)
+
+            def call():
+                if kind == "norm":
+                    N.call("ns_linear_forward_norm_quant", dev.handle, lin, C.c_uint64(xq.ptr), C.c_uint64(xs.ptr), res.ptr, C.c_int64(rows_m), y.ptr,
+                           gam.ptr, bet.ptr, C.c_float(1e-5), q.ptr, sc.ptr)
+                else:
+                    N.call("ns_linear_forward_gelu_quant", dev.handle, lin, C.c_uint64(xq.ptr), C.c_uint64(xs.ptr), C.c_int64(rows_m), q.ptr, sc.ptr)
+            for _ in range(5):
+                call()
+            dev.synchronize()
+            N.call("ns_debug_tail_times", dev.handle, C.c_uint64(times.ptr))
+            call()
+            dev.synchronize()
+            N.call("ns_debug_tail_times", dev.handle, C.c_uint64(0))
+            t = times.download().view(np.uint64).reshape(-1, 4).astype(np.int64)
+            t = t[t[:, 0] > 0]
+            rel = (t - t[:, 0].min()) / 1000.0
+            waited = rel[rel[:, 3] > 0]
+            e0, e1 = dev.event(), dev.event()
+            dev.record(e0)
+            for _ in range(50):
+                call()
+            dev.record(e1)
+            out.append({"kind": kind, "M": rows_m, "K": k_, "N": n_, "ctas": int(len(t)), "row_ctas": int(len(waited)),
+                        "product_done_us": [float(rel[:, 1].min()), float(rel[:, 1].max())],
+                        "all_arrived_us": [float(rel[rel[:, 2] > 0][:, 2].min()), float(rel[:, 2].max())],
+                        "rows_done_us": [float(waited[:, 3].min()), float(waited[:, 3].max())],
+                        "us_per_call_back_to_back": dev.elapsed_ms(e0, e1) / 50 * 1e3})
+            N.call("ns_memset32_async", dev.handle, C.c_uint64(times.ptr), 0, C.c_uint64(148 * 8))
+            dev.synchronize()
+            N.call("ns_linear_destroy", lin)
+        print(json.dumps({"case": spec, "ok": True, "phases": out}))
+        return
+    elif name == "decode_shapes":
+        # The weight-streaming products of the benchmark configurations, each as a graph of 20 launches over rotating weight copies
+        # (more than the 126 MB of L2 in total, so every launch streams from HBM), and the same graph of an empty kernel
+        # (ns_add_i32 of one thread): the launch floor a product of a few microseconds sits on.
+        peaks = measured_peaks()
+        reps = 20
+        e0, e1 = dev.event(), dev.event()
+
+        def timed_graph(launch):
+            for i in range(reps):
+                launch(i)
+            dev.synchronize()
+            dev.capture_begin()
+            for i in range(reps):
+                launch(i)
+            g = dev.capture_end()
+            for _ in range(3):
+                dev.graph_launch(g)
+            dev.synchronize()
+            best = None
+            for _ in range(5):
+                dev.record(e0)
+                dev.graph_launch(g)
+                dev.record(e1)
+                us = dev.elapsed_ms(e0, e1) / reps * 1e3
+                best = us if best is None else min(best, us)
+            dev.graph_destroy(g)
+            return best
+
+        counter = dev.zeros(1, N.NS_I32)
+        floor_us = timed_graph(lambda i: N.call("ns_add_i32", dev.handle, counter.ptr, 0))
+        rows = []
+        shapes = [("i8", 1, 4096, 4096), ("i8", 16, 4096, 4096), ("i8", 128, 4096, 4096), ("bf16", 8, 14336, 4096),
+                  ("i8", 64, 6144, 2048), ("i8", 64, 2048, 2048), ("i8", 64, 8192, 2048), ("i8", 64, 2048, 8192), ("i8", 64, 32000, 2048)]
+        for kind, m, n_, k_ in shapes:
+            el = 1 if kind == "i8" else 2
+            copies = max(2, min(reps, -(-160_000_000 // (n_ * k_ * el))))
+            ws = []
+            for c in range(copies):
+                w = dev.empty(n_ * k_, N.NS_I8 if kind == "i8" else N.NS_BF16)
+                N.call("ns_fill_normal", dev.handle, w.ptr, N.NS_I8 if kind == "i8" else N.NS_BF16, C.c_int64(n_ * k_), 9 + c, 0.0, 40.0 if kind == "i8" else 1.0)
+                ws.append(w)
+            if kind == "i8":
+                a = dev.empty(m * k_, N.NS_I8)
+                N.call("ns_fill_normal", dev.handle, a.ptr, N.NS_I8, C.c_int64(m * k_), 1, 0.0, 40.0)
+                a_s, w_s, b = dev.empty(m), dev.empty(n_), dev.empty(n_)
+                for t, cnt in ((a_s, m), (w_s, n_), (b, n_)):
+                    N.call("ns_fill_normal", dev.handle, t.ptr, N.NS_F32, C.c_int64(cnt), 5, 1.0, 0.1)
+                y = dev.empty(m * n_)
+                us = timed_graph(lambda i: N.call("ns_qmatmul_i8", dev.handle, a.ptr, a_s.ptr, ws[i % copies].ptr, w_s.ptr, b.ptr, 0, 0, m, n_, k_,
+                                                  N.EPI_BIAS, N.NS_F32, y.ptr, 0))
+                nbytes = n_ * k_ + m * k_ + 4 * m * n_ + 4 * (m + 2 * n_)
+            else:
+                a = dev.empty(m * k_, N.NS_BF16)
+                N.call("ns_fill_normal", dev.handle, a.ptr, N.NS_BF16, C.c_int64(m * k_), 1, 0.0, 1.0)
+                y = dev.empty(m * n_, N.NS_BF16)
+                us = timed_graph(lambda i: N.call("ns_matmul_bf16", dev.handle, a.ptr, ws[i % copies].ptr, y.ptr, 1, m, n_, k_, 0, 0, 0, 0, N.EPI_NONE,
+                                                  N.NS_BF16))
+                nbytes = 2 * (m * k_ + k_ * n_ + m * n_)
+            gbs = nbytes / (us * 1e-6) / 1e9
+            net = nbytes / (max(us - floor_us, 1e-3) * 1e-6) / 1e9
+            rows.append({"kind": kind, "M": m, "N": n_, "K": k_, "us": us, "algorithmic_bytes": nbytes, "gbs": gbs, "hbm_frac": gbs / peaks["hbm"],
+                         "hbm_time_us": nbytes / peaks["hbm"] / 1e3, "hbm_frac_net_of_launch_floor": net / peaks["hbm"], "weight_copies": copies})
+            for w in ws:
+                w.release()
+        print(json.dumps({"case": spec, "ok": True, "launch_floor_us": floor_us, "hbm_peak_gbs": peaks["hbm"], "shapes": rows}))
+        return
     elif name == "attention_decode":
         B, heads, dh, L, ps = 64, 32, 128, int(arg or 1024), 64
         max_pages = (L + ps) // ps
@@ -654,10 +780,11 @@ def run_case(spec: str):
             N.call("ns_attention_prefill", dev.handle, q.ptr, k.ptr, v.ptr, o.ptr, B, H, S, 128, st, st, st, st, C.c_float(0.0884), 1)
     elif name == "gpt_decode":
         from nn_b200 import dist as nsdist
-        parts = arg.split(":") + ["", "", "", ""]
+        parts = arg.split(":") + ["", "", "", "", ""]
         rank, world, _ = nsdist.env_rank()
         rec = run_gpt_decode(dev, rank, world, measured_peaks(), int(parts[0] or 2), int(parts[1] or 64), compare_tp1=False,
-                             fused=int(parts[2]) if parts[2] else None, attn_quant=bool(int(parts[3])) if parts[3] else None)
+                             fused=int(parts[2]) if parts[2] else None, attn_quant=bool(int(parts[3])) if parts[3] else None,
+                             batch=int(parts[4]) if parts[4] else None)
         if rank == 0:
             print(json.dumps({"case": spec, "ok": True, "gpt_decode": rec}))
         return

@@ -80,7 +80,9 @@ NS_API int ns_device_status(ns_device_t dev, int* status);
 /* TEST HOOK, not for hosts: overrides the products' tiling heuristic so that tests and profiler cases can reach
  * every kernel variant on one shape.  tile_n: 0 = heuristic, 64 / 128 / 256 = that tile width with the single-CTA
  * kernel, NS_TUNE_NARROW = the narrowest tile, NS_TUNE_PAIR = the CTA-pair kernel wherever a shape allows it.
- * k_splits: 0 = heuristic, otherwise the split-K count.  A host binding has no reason to import this. */
+ * k_splits: 0 = heuristic, otherwise the split-K count; with NS_TUNE_PAIR, 2 = the pair kernel with its tiles' k-blocks dealt
+ * out to the clusters in equal shares (the form large products take when their last wave of tiles would leave many clusters
+ * idle), on any shape of at least four tiles.  A host binding has no reason to import this. */
 /* TEST HOOK, not for hosts: while `buffer` (device memory, 4 x 8 bytes per SM) is non-zero, every CTA of a product with a
  * second phase (ns_linear_forward_norm_quant and its siblings) records four times in nanoseconds there: kernel start,
  * product done, all CTAs arrived, rows done.  0 turns it off. */
@@ -280,10 +282,12 @@ NS_API int ns_kv_cache_destroy(ns_kv_cache_t cache);
  * all heads of this rank's n_seqs sequences (global sequence numbers seq0 ..); for each of them the first pages_used pages of
  * every head are copied into the cache of the rank that owns the head (heads / world consecutive heads per rank):
  * dst_k_pools / dst_v_pools are the `world` ranks' pools as mapped in this process (its own pool at its own rank),
- * dst_table the page table the destination caches share.  Plain 16-byte stores over NVLink; queued on the stream. */
+ * dst_table the page table the destination caches share.  `layers` > 1 copies that many layers in the one launch: `src` and
+ * the pool addresses are layer 0's, the pools of layer l lie l * src_layer_stride / dst_layer_stride BYTES further on (all
+ * layers of a model in one allocation, same geometry and page tables).  Plain 16-byte stores over NVLink; queued on the stream. */
 NS_API int ns_kv_scatter_heads(ns_device_t dev, ns_kv_cache_t src, uint64_t src_table, int src_max_pages, int n_seqs, int seq0, int pages_used,
                                const uint64_t* dst_k_pools, const uint64_t* dst_v_pools, int world, int dst_heads, int dst_num_pages,
-                               uint64_t dst_table, int dst_max_pages);
+                               uint64_t dst_table, int dst_max_pages, int layers, uint64_t src_layer_stride, uint64_t dst_layer_stride);
 NS_API int ns_kv_cache_pools(ns_kv_cache_t cache, uint64_t* k_pool, uint64_t* v_pool, uint64_t* bytes_each);
 
 /* cache[b, pos + i, h, :] = k/v[(b * steps + i) * src_stride + h * head_dim + :] for i < steps; pos is an int32 in

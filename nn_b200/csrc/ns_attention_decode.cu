@@ -462,6 +462,8 @@ struct KvScatterParams {
     int dst_max_pages, dst_heads, dst_num_pages;
     int n_seqs, seq0, pages_used, world;
     int slab_vec;                 // 16-byte vectors per slab
+    int layers;                   // the pools of layer l sit l * src_layer_vec / dst_layer_vec 16-byte vectors after layer 0's
+    size_t src_layer_vec, dst_layer_vec;
     int* status;
 };
 
@@ -470,7 +472,10 @@ __global__ void __launch_bounds__(256) ns_kv_scatter_heads_kernel(const KvScatte
     ns_pdl_wait();
     ns_pdl_trigger();
     const int slabs = p.n_seqs * p.pages_used * p.src_heads;
-    for (int s = blockIdx.x; s < slabs; s += gridDim.x) {
+    const long long total = (long long)slabs * p.layers;
+    for (long long w = blockIdx.x; w < total; w += gridDim.x) {
+        const int layer = (int)(w / slabs);
+        const int s = (int)(w % slabs);
         const int h = s % p.src_heads;
         const int j = (s / p.src_heads) % p.pages_used;
         const int b = s / (p.src_heads * p.pages_used);
@@ -481,8 +486,8 @@ __global__ void __launch_bounds__(256) ns_kv_scatter_heads_kernel(const KvScatte
             if (threadIdx.x == 0) *reinterpret_cast<volatile int*>(p.status) = 510;
             continue;
         }
-        const size_t so = ((size_t)sp * p.src_heads + h) * p.slab_vec;
-        const size_t dofs = ((size_t)dp * p.dst_heads + hl) * p.slab_vec;
+        const size_t so = ((size_t)sp * p.src_heads + h) * p.slab_vec + (size_t)layer * p.src_layer_vec;
+        const size_t dofs = ((size_t)dp * p.dst_heads + hl) * p.slab_vec + (size_t)layer * p.dst_layer_vec;
         const uint4* sk = reinterpret_cast<const uint4*>(p.src_k) + so;
         const uint4* sv = reinterpret_cast<const uint4*>(p.src_v) + so;
         uint4* dk = reinterpret_cast<uint4*>(p.dst_k[r]) + dofs;
@@ -498,7 +503,7 @@ __global__ void __launch_bounds__(256) ns_kv_scatter_heads_kernel(const KvScatte
 
 extern "C" int ns_kv_scatter_heads(ns_device_t h, ns_kv_cache_t src, uint64_t src_table, int src_max_pages, int n_seqs, int seq0, int pages_used,
                                    const uint64_t* dst_k_pools, const uint64_t* dst_v_pools, int world, int dst_heads, int dst_num_pages,
-                                   uint64_t dst_table, int dst_max_pages)
+                                   uint64_t dst_table, int dst_max_pages, int layers, uint64_t src_layer_stride, uint64_t dst_layer_stride)
 {
     NsDevice* d = ns_dev(h);
     int rc = ns_device_make_current(d);
@@ -509,6 +514,8 @@ extern "C" int ns_kv_scatter_heads(ns_device_t h, ns_kv_cache_t src, uint64_t sr
                "ns_kv_scatter_heads: %d ranks x %d heads do not make the source's %d heads", world, dst_heads, c->heads);
     NS_REQUIRE(n_seqs >= 0 && seq0 >= 0 && pages_used >= 0 && pages_used <= src_max_pages && pages_used <= dst_max_pages, NS_ERR_ARGUMENT,
                "ns_kv_scatter_heads: bad shape");
+    NS_REQUIRE(layers >= 1 && (layers == 1 || (src_layer_stride % 16 == 0 && dst_layer_stride % 16 == 0 && src_layer_stride > 0 && dst_layer_stride > 0)),
+               NS_ERR_ARGUMENT, "ns_kv_scatter_heads: layer strides must be positive multiples of 16 bytes");
     if (n_seqs == 0 || pages_used == 0) return NS_OK;
     KvScatterParams p;
     memset(&p, 0, sizeof(p));
@@ -525,8 +532,11 @@ extern "C" int ns_kv_scatter_heads(ns_device_t h, ns_kv_cache_t src, uint64_t sr
     p.dst_max_pages = dst_max_pages; p.dst_heads = dst_heads; p.dst_num_pages = dst_num_pages;
     p.n_seqs = n_seqs; p.seq0 = seq0; p.pages_used = pages_used; p.world = world;
     p.slab_vec = c->page_size * c->head_dim * 2 / 16;
+    p.layers = layers;
+    p.src_layer_vec = src_layer_stride / 16;
+    p.dst_layer_vec = dst_layer_stride / 16;
     p.status = d->status_dev;
-    const int64_t slabs = (int64_t)n_seqs * pages_used * c->heads;
+    const int64_t slabs = (int64_t)n_seqs * pages_used * c->heads * layers;
     const int64_t cap = (int64_t)d->sm_count * 8;
     NS_CUDA(ns_launch_plain(ns_kv_scatter_heads_kernel, dim3((unsigned)(slabs < cap ? slabs : cap)), dim3(256), 0, d->stream, p));
     return NS_OK;

@@ -27,6 +27,12 @@ struct NsGemmParams {
     const float* bias;
     const void* residual;
     void* partial;      // [k_splits, M, N] 32-bit words when k_splits > 1
+    // CTA-pair kernel with its tiles' k-blocks dealt out evenly to the clusters (see ns_gemm_pair_kernel): total k-block
+    // units = tiles * k_blocks; a tile that straddles two clusters leaves one part's accumulators in sk_work
+    // [clusters, 256, 256] 32-bit words and a count of finished epilogue warps in sk_flags [clusters]
+    int streamk;
+    uint32_t* sk_work;
+    uint32_t* sk_flags;
     int* status;
     int status_base;    // code = status_base + role
 };

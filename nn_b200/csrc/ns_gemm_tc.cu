@@ -150,6 +150,10 @@ struct EpiCtx {
     uint32_t bufs;   // two staging buffers (one when `single`)
     int nbuf;        // stores queued so far (selects the buffer)
     bool single;     // one staging buffer: a second warp on the same scheduler covers the wait for its store
+    // a tile shared by two clusters (pair kernel, k-blocks dealt out evenly):
+    int sk_dump;               // >= 0: this part's accumulators go to slab sk_dump of the work area instead of the output
+    const uint32_t* sk_add;    // non-null: the other part's accumulators of this thread's row (256 words), added before the epilogue
+    int sk_row, sk_col;        // first row of this warp and first column of the chunk inside the 256 x 256 tile
 };
 
 // Finishes 32 columns [col0, col0+32) of this thread's row from accumulator words r and sends them out.
@@ -159,6 +163,11 @@ template <int KIND>
 __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const StoreMaps& sm, EpiCtx& cx, const uint32_t (&r)[32], int col0)
 {
     const size_t base = (size_t)cx.row * p.N + col0;
+    if (cx.sk_dump >= 0) {
+        stage_and_store<32>(cx.bufs + (cx.single ? 0 : (cx.nbuf & 1)) * EPI_BUF_BYTES, cx.lane, r, &sm.part, cx.sk_col, cx.sk_row, cx.sk_dump, true, cx.single);
+        cx.nbuf++;
+        return;
+    }
     if (p.k_splits > 1) {
         if (p.tma_store) {
             stage_and_store<32>(cx.bufs + (cx.single ? 0 : (cx.nbuf & 1)) * EPI_BUF_BYTES, cx.lane, r, &sm.part, col0, cx.row0, cx.split, true, cx.single);
@@ -418,6 +427,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
         cx.bufs = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
         cx.nbuf = 0;
         cx.single = false;
+        cx.sk_dump = -1; cx.sk_add = nullptr; cx.sk_row = 0; cx.sk_col = 0;
         int local = 0;
         bool ok = true;
         ns_pdl_wait();   // a_scale, residual and every output buffer belong to the previous kernel until it is done
@@ -556,6 +566,64 @@ __device__ __forceinline__ void pair_coords(const NsGemmParams& p, int item, int
 
 constexpr int PAIR_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
 
+// r += the other part's accumulators of the same 32 columns (a tile shared by two clusters).  Exact for int32; float
+// accumulators are added in a fixed order (this part + the other part), so results do not depend on timing.
+template <int KIND>
+__device__ __forceinline__ void add_other_part(uint32_t (&r)[32], const uint32_t* __restrict__ src)
+{
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        const uint4 t = __ldcg(s4 + q);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            r[4 * q + j] = KIND == NS_KIND_I8 ? (uint32_t)((int32_t)r[4 * q + j] + (int32_t)w[j])
+                                              : __float_as_uint(__fadd_rn(__uint_as_float(r[4 * q + j]), __uint_as_float(w[j])));
+    }
+}
+
+// The work of cluster `cluster` of `n_clusters`.  Plain mode: tiles cluster, cluster + n_clusters, ... whole.  Even mode
+// (p.streamk): the tiles' k-blocks are numbered through (tile-major) and dealt out in equal contiguous shares, so a
+// share begins with the LAST k-blocks of one tile, continues with whole tiles and ends with the FIRST k-blocks of
+// another.  The cluster that holds a tile's first k-blocks finishes the tile (it reaches them last); the one that
+// holds its last k-blocks computes them first and leaves the accumulators in the work area.
+struct PairWork {
+    int count;          // items of this cluster
+    int first;          // first tile (even mode)
+    long long u0, u1;   // unit range (even mode)
+};
+__device__ __forceinline__ PairWork pair_work(const NsGemmParams& p, int cluster, int n_clusters, int n_items)
+{
+    PairWork w;
+    if (!p.streamk) {
+        w.count = cluster < n_items ? (n_items - cluster + n_clusters - 1) / n_clusters : 0;
+        w.first = cluster; w.u0 = 0; w.u1 = 0;
+        return w;
+    }
+    const long long total = (long long)n_items * p.k_blocks;
+    w.u0 = total * cluster / n_clusters;
+    w.u1 = total * (cluster + 1) / n_clusters;
+    w.first = (int)(w.u0 / p.k_blocks);
+    w.count = w.u1 > w.u0 ? (int)((w.u1 - 1) / p.k_blocks) - w.first + 1 : 0;
+    return w;
+}
+// item i of the cluster: tile, k-block range, and what happens to the accumulators (0 = finish as usual, 1 = leave them
+// in the work area (slab = cluster), 2 = add the part the NEXT cluster left in slab cluster + 1, then finish)
+__device__ __forceinline__ void pair_item(const NsGemmParams& p, const PairWork& w, int cluster, int n_clusters, int i, int& tile, int& kb0, int& kb1,
+                                          int& role)
+{
+    if (!p.streamk) {
+        tile = cluster + i * n_clusters; kb0 = 0; kb1 = p.k_blocks; role = 0;
+        return;
+    }
+    tile = w.first + i;
+    const long long t0 = (long long)tile * p.k_blocks;
+    kb0 = (int)(w.u0 > t0 ? w.u0 - t0 : 0);
+    kb1 = (int)(w.u1 < t0 + p.k_blocks ? w.u1 - t0 : p.k_blocks);
+    role = kb0 > 0 ? 1 : (kb1 < p.k_blocks ? 2 : 0);
+}
+
 template <int KIND, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -583,6 +651,7 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int cluster = blockIdx.x >> 1;
     const int n_clusters = gridDim.x >> 1;
     const int n_items = p.tiles_m * p.tiles_n;
+    const PairWork work = pair_work(p, cluster, n_clusters, n_items);
 
     if (threadIdx.x == 0) {
         abort_flag_storage = 0;
@@ -620,12 +689,13 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int item = cluster; item < n_items && ok; item += n_clusters) {
-                int tm, tn;
+            for (int i = 0; i < work.count && ok; i++) {
+                int item, kb0, kb1, role, tm, tn;
+                pair_item(p, work, cluster, n_clusters, i, item, kb0, kb1, role);
                 pair_coords(p, item, tm, tn);
                 const int row0 = tm * 256 + (int)rank * BM;
                 const int brow0 = tn * BN + (int)rank * Cfg::BN_HALF;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
+                for (int kb = kb0; kb < kb1; kb++) {
                     ok = ns_mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, p.status, p.status_base + 11);
                     if (!ok) break;
                     // the even CTA's barrier counts the four boxes of the pair (boxes that reach past the matrix
@@ -660,14 +730,16 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
-            for (int item = cluster; item < n_items && ok; item += n_clusters, local++) {
+            for (int i = 0; i < work.count && ok; i++, local++) {
+                int item, kb0, kb1, role;
+                pair_item(p, work, cluster, n_clusters, i, item, kb0, kb1, role);
                 const int acc = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
                 ok = ns_mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, p.status_base + 12);
                 if (!ok) break;
                 ns_tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
+                for (int kb = kb0; kb < kb1; kb++) {
                     ok = ns_mbar_wait(full_bar(s), phase, abort_flag, p.status, p.status_base + 13);
                     if (!ok) break;
                     ns_tc_fence_after();
@@ -677,7 +749,7 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (int kk = 0; kk < 4; kk++) {
                         const uint64_t a_desc = ns_desc_at(desc_k, a_addr + kk * 32);
                         const uint64_t b_desc = B_MN ? ns_desc_at(desc_mn, b_addr + kk * (16 * 128)) : ns_desc_at(desc_k, b_addr + kk * 32);
-                        const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+                        const uint32_t accumulate = (kb > kb0 || kk > 0) ? 1u : 0u;
                         if (KIND == NS_KIND_I8) ns_mma_i8_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
                         else ns_mma_f16_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
                     }
@@ -701,12 +773,19 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         cx.nbuf = 0;
         cx.single = true;
         cx.split = 0;
+        cx.sk_dump = -1; cx.sk_add = nullptr; cx.sk_row = 0; cx.sk_col = 0;
         int local = 0;
         bool ok = true;
         const uint32_t tempty_even0 = ns_mapa(tempty_bar(0), 0), tempty_even1 = ns_mapa(tempty_bar(1), 0);
-        for (int item = cluster; item < n_items && ok; item += n_clusters, local++) {
-            int tm, tn;
+        for (int i = 0; i < work.count && ok; i++, local++) {
+            int item, kb0, kb1, role, tm, tn;
+            pair_item(p, work, cluster, n_clusters, i, item, kb0, kb1, role);
             pair_coords(p, item, tm, tn);
+            // a tile shared with a neighbouring cluster: its last k-blocks (computed here first) go to the work area, or its
+            // first k-blocks (computed here last) are completed with what the next cluster left there
+            cx.sk_dump = role == 1 ? cluster : -1;
+            cx.sk_row = (int)rank * BM + quad * 32;
+            const uint32_t* other_part = role == 2 ? p.sk_work + ((size_t)(cluster + 1) * 256 + cx.sk_row + lane) * 256 : nullptr;
             const int acc = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             cx.row0 = tm * 256 + (int)rank * BM + quad * 32;
@@ -724,6 +803,26 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             ns_tc_fence_after();
+            if (role == 2) {
+                // the next cluster computed its part of this tile first of all, long ago; the wait is bounded all the same
+                if (lane == 0) {
+                    const long long t0 = clock64();
+                    uint32_t seen;
+                    for (;;) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.sk_flags + cluster + 1) : "memory");
+                        if (seen >= 16u) break;
+                        if (*abort_flag != 0 || clock64() - t0 > NS_WAIT_LIMIT_CYCLES) {
+                            *reinterpret_cast<volatile int*>(p.status) = p.status_base + 16;
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(64);
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
             const uint32_t t_row = tmem_base + (uint32_t(quad * 32) << 16) + acc * BN;
             const bool warp_has_rows = cx.row0 < p.M;
             uint32_t ra[32];
@@ -733,11 +832,24 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 ns_tmem_ld32(t_row + c * 32, ra);
                 ns_tc_wait_ld();
                 __syncwarp();
-                if (warp_has_rows && tn * BN + c * 32 < p.N) epilogue_chunk<KIND>(p, sm, cx, ra, tn * BN + c * 32);
+                if (warp_has_rows && tn * BN + c * 32 < p.N) {
+                    cx.sk_col = c * 32;
+                    if (other_part != nullptr) add_other_part<KIND>(ra, other_part + c * 32);
+                    epilogue_chunk<KIND>(p, sm, cx, ra, tn * BN + c * 32);
+                }
             }
             ns_tc_fence_before();
             __syncwarp();
             if (lane == 0) ns_mbar_arrive_cluster(acc ? tempty_even1 : tempty_even0);
+            if (role == 1) {
+                // this warp's share of the part is in the work area once its stores are complete: count it in
+                if (lane == 0) {
+                    ns_bulk_wait<0>();
+                    __threadfence();
+                    atomicAdd(p.sk_flags + cluster, 1u);
+                }
+                __syncwarp();
+            }
         }
         if (lane == 0) ns_bulk_wait_read<0>();
         __syncwarp();
@@ -845,7 +957,7 @@ int launch_gemm(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, con
 }
 
 template <int KIND, bool B_MN>
-int launch_pair(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p)
+int pair_max_clusters(NsDevice* d, int* out)
 {
     auto kernel = ns_gemm_pair_kernel<KIND, B_MN>;
     static int max_clusters[64] = {0};
@@ -866,8 +978,14 @@ int launch_pair(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, con
         if (n > d->sm_count / 2) n = d->sm_count / 2;
         max_clusters[d->ordinal] = n;
     }
-    const int items = p.tiles_m * p.tiles_n;
-    const int clusters = items < max_clusters[d->ordinal] ? items : max_clusters[d->ordinal];
+    *out = max_clusters[d->ordinal];
+    return NS_OK;
+}
+
+template <int KIND, bool B_MN>
+int launch_pair(NsDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const StoreMaps& sm, const NsGemmParams& p, int clusters)
+{
+    auto kernel = ns_gemm_pair_kernel<KIND, B_MN>;
     NS_CUDA(ns_launch_plain(kernel, dim3(2 * clusters), dim3(PAIR_THREADS), PairCfg::SMEM_BYTES, d->stream, tmA, tmB, sm, p));
     return NS_OK;
 }
@@ -952,11 +1070,42 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
         splits = 1;
         if (d->force_bn == 0) bn = 64;
     }
+    if (d->force_bn == NS_TUNE_PAIR && d->force_splits == 2) splits = 1;   // test hook: pair kernel, k-blocks dealt out evenly
     const bool pair = tail == nullptr && splits == 1 && M > BM && (d->force_bn == NS_TUNE_PAIR || (d->force_bn == 0 && bn == 256));
     p.kb_per_split = (p.k_blocks + splits - 1) / splits;
     p.k_splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
     p.tiles_m = pair ? (M + 255) / 256 : (M + BM - 1) / BM;
     p.tiles_n = (N + bn - 1) / bn;
+    // CTA-pair kernel: how many clusters, and whether the last wave would leave many of them idle.  128 tiles on 74
+    // clusters are 1.73 waves that take the time of 2: then the tiles' k-blocks are dealt out evenly instead (every
+    // cluster gets tiles * k_blocks / clusters of them; a tile that straddles two clusters is completed through a work
+    // area).  The test hook NS_TUNE_PAIR with a split count of 2 forces that mode on small shapes.
+    int pair_clusters = 0;
+    p.streamk = 0;
+    p.sk_work = nullptr;
+    p.sk_flags = nullptr;
+    if (pair) {
+        int max_c = 0;
+        int prc = kind == NS_KIND_I8 ? pair_max_clusters<NS_KIND_I8, false>(d, &max_c)
+                  : (!b_is_kn ? pair_max_clusters<NS_KIND_BF16, false>(d, &max_c) : pair_max_clusters<NS_KIND_BF16, true>(d, &max_c));
+        if (prc != NS_OK) return prc;
+        const int items = p.tiles_m * p.tiles_n;
+        pair_clusters = items < max_c ? items : max_c;
+        const bool forced = d->force_bn == NS_TUNE_PAIR && d->force_splits == 2 && items >= 3 && p.k_blocks >= 2;
+        if (forced) pair_clusters = (items * 3 + 3) / 4 < max_c ? (items * 3 + 3) / 4 : max_c;
+        const int waves = (items + pair_clusters - 1) / pair_clusters;
+        const bool uneven = items > pair_clusters && (int64_t)items * 100 < (int64_t)waves * pair_clusters * 93;
+        if ((uneven && p.k_blocks >= 8) || (forced && pair_clusters < items)) {
+            const size_t work_bytes = (size_t)(pair_clusters + 1) * 256 * 256 * 4;
+            void* block = nullptr;
+            int src = ns_scratch_reserve(d, work_bytes + 4096, &block);
+            if (src != NS_OK) return src;
+            p.streamk = 1;
+            p.sk_work = reinterpret_cast<uint32_t*>(block);
+            p.sk_flags = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(block) + work_bytes);
+            NS_CUDA(cudaMemsetAsync(p.sk_flags, 0, 4096, d->stream));
+        }
+    }
     p.status = d->status_dev;
     p.status_base = kind == NS_KIND_I8 ? 100 : 200;
     p.partial = nullptr;
@@ -1019,6 +1168,13 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     }
     p.tma_store = tma_ok ? 1 : 0;
     p.vec_cols = ((reinterpret_cast<uintptr_t>(p.w_scale) | reinterpret_cast<uintptr_t>(p.bias)) & 15) == 0 ? 1 : 0;
+    if (p.streamk) {
+        uint64_t dims[3] = {256, 256, (uint64_t)(pair_clusters + 1)};
+        uint64_t strides[2] = {256 * 4, 256 * 256 * 4};
+        uint32_t box[3] = {32, 32, 1};
+        rc = ns_make_tensor_map(&sm.part, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, p.sk_work, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != NS_OK) return rc;
+    }
     if (tma_ok) {
         if (p.k_splits > 1) {
             uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)p.k_splits};
@@ -1058,9 +1214,9 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
         }
     }
     if (pair) {
-        if (kind == NS_KIND_I8) rc = launch_pair<NS_KIND_I8, false>(d, tmA, tmB, sm, p);
-        else if (!b_is_kn) rc = launch_pair<NS_KIND_BF16, false>(d, tmA, tmB, sm, p);
-        else rc = launch_pair<NS_KIND_BF16, true>(d, tmA, tmB, sm, p);
+        if (kind == NS_KIND_I8) rc = launch_pair<NS_KIND_I8, false>(d, tmA, tmB, sm, p, pair_clusters);
+        else if (!b_is_kn) rc = launch_pair<NS_KIND_BF16, false>(d, tmA, tmB, sm, p, pair_clusters);
+        else rc = launch_pair<NS_KIND_BF16, true>(d, tmA, tmB, sm, p, pair_clusters);
     }
     else if (kind == NS_KIND_I8) rc = dispatch_bn<NS_KIND_I8, false>(d, bn, tmA, tmB, sm, p);
     else if (!b_is_kn) rc = dispatch_bn<NS_KIND_BF16, false>(d, bn, tmA, tmB, sm, p);

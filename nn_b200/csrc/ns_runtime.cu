@@ -176,6 +176,9 @@ extern "C" int ns_stream_sync(ns_device_t h)
     int st = d->status_host[0];
     if (st != 0) {
         d->status_host[0] = 0;
+        // a kernel that gave up may have left the arrival counters of the one-launch products half-way: start clean
+        if (d->sync_words != nullptr && cudaMemsetAsync(d->sync_words, 0, NS_SYNC_WORDS * sizeof(uint32_t), d->stream) == cudaSuccess)
+            cudaStreamSynchronize(d->stream);
         return ns_fail(NS_ERR_KERNEL, "a kernel gave up a bounded wait (status %d: kernel %d, role %d)", st, st / 100, st % 100);
     }
     return NS_OK;

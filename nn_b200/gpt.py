@@ -129,6 +129,7 @@ class GptW8A8:
             self.caches.append(h)
         self.replica = None            # a one-GPU model of batch / tp sequences for the batch-sharded prompt read
         self._peer_kv = None           # every rank's kv_block as mapped here
+        self._bar = None
         # activations (sized for the longest prefill) and device-side state
         R = self.max_rows
         self.x = [dev.empty(R * D, N.NS_BF16), dev.empty(R * D, N.NS_BF16)]
@@ -484,17 +485,20 @@ class GptW8A8:
         from . import dist
         rep, bl, t = self.replica, self.batch // self.tp, ids.shape[1]
         h = self.dev.handle
-        # every rank must be done with its previous step (it reads its cache) before a peer overwrites that cache
-        self.dev.synchronize()
-        dist.barrier()
+        # Every rank must be done with its previous step (it reads its cache) before a peer overwrites that cache: a one-word
+        # all-reduce queued on the stream completes on a rank only once every rank has reached it in its own stream.
+        if self._bar is None:
+            self._bar = self.dev.zeros(8, N.NS_I32)
+        N.call("ns_allreduce", h, self.comm, C.c_uint64(self._bar.ptr), C.c_int64(1), N.NS_I32)
         rep.prefill(ids[self.rank * bl:(self.rank + 1) * bl])
         pages_used = (t + self.page_size - 1) // self.page_size
+        # one launch for all layers: both models keep [layer][keys, values] pools in one allocation
         arr = C.c_uint64 * self.tp
-        for i, cache in enumerate(rep.caches):
-            dk = arr(*[p + 2 * i * self.pool_bytes for p in self._peer_kv])
-            dv = arr(*[p + (2 * i + 1) * self.pool_bytes for p in self._peer_kv])
-            N.call("ns_kv_scatter_heads", h, cache, rep.page_table.ptr, rep.max_pages, bl, self.rank * bl, pages_used, dk, dv, self.tp, self.heads_loc,
-                   self.batch * self.max_pages, self.page_table.ptr, self.max_pages)
+        dk = arr(*self._peer_kv)
+        dv = arr(*[p + self.pool_bytes for p in self._peer_kv])
+        N.call("ns_kv_scatter_heads", h, rep.caches[0], rep.page_table.ptr, rep.max_pages, bl, self.rank * bl, pages_used, dk, dv, self.tp, self.heads_loc,
+               self.batch * self.max_pages, self.page_table.ptr, self.max_pages, self.cfg.layers, C.c_uint64(2 * rep.pool_bytes),
+               C.c_uint64(2 * self.pool_bytes))
         # the first tokens of all sequences; a rank's share leaves only after its stores above are complete (stream order), and
         # the gather completes only when every rank has contributed: after it, every cache holds every sequence's prompt
         N.call("ns_allgather", h, self.comm, C.c_uint64(rep.ids.ptr), C.c_uint64(self.ids.ptr), C.c_int64(bl), N.NS_I32)

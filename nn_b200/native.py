@@ -69,7 +69,7 @@ SIGNATURES = {
     "ns_kv_cache_create": [vp, i32, i32, i32, i32, P(vp)],
     "ns_kv_cache_create_in": [vp, i32, i32, i32, i32, u64, u64, P(vp)],
     "ns_kv_cache_destroy": [vp],
-    "ns_kv_scatter_heads": [vp, vp, u64, i32, i32, i32, i32, P(u64), P(u64), i32, i32, i32, u64, i32],
+    "ns_kv_scatter_heads": [vp, vp, u64, i32, i32, i32, i32, P(u64), P(u64), i32, i32, i32, u64, i32, i32, u64, u64],
     "ns_kv_cache_pools": [vp, P(u64), P(u64), P(u64)],
     "ns_kv_append": [vp, vp, u64, u64, i64, u64, i32, u64, i32, i32],
     "ns_attention_decode": [vp, vp, u64, i64, u64, i64, u64, i32, u64, i32, i32, f32],

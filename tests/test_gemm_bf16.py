@@ -114,3 +114,21 @@ def test_chained_products_without_synchronisation(dev, orc):
         c1_host = c1.download((m, n))
         exp = orc.matmul_bf16(dmat, c1_host, b_is_nk=False)
         assert orc.close(exp, c2.download((m2, n)), 1e-4), f"repetition {rep}: the second product read B before it was written"
+
+
+@pytest.mark.parametrize("transB", [False, True])
+@pytest.mark.parametrize("m,n,k", [(700, 264, 512), (1024, 768, 1024)])
+def test_cta_pair_kernel_with_k_blocks_dealt_out_evenly(dev, orc, m, n, k, transB):
+    """The pair kernel with the tiles' k-blocks dealt out in equal shares (see the int8 test of the same name): float
+    accumulators of a shared tile are added in a fixed order, so two runs agree bit for bit and with the oracle to 1e-4."""
+    a = orc.round_bf16(orc.normal((m, k), 33))
+    b = orc.round_bf16(orc.normal((n, k) if transB else (k, n), 34))
+    dev.tune(512, 2)
+    try:
+        c1 = _run(dev, a, b, m, n, k, transB, out_dtype=N.NS_F32)[0]
+        c2 = _run(dev, a, b, m, n, k, transB, out_dtype=N.NS_F32)[0]
+    finally:
+        dev.tune(0, 0)
+    exp = orc.matmul_bf16(a, b, b_is_nk=transB)
+    assert orc.close(exp, c1, 1e-4), f"max err {orc.max_err(exp, c1)}"
+    assert np.array_equal(c1.view(np.uint32), c2.view(np.uint32))

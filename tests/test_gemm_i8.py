@@ -209,3 +209,27 @@ def test_equals_the_reference_float_linear_on_dequantised_operands(dev, orc, M):
     # that worst-case bound is loose (a few per cent of a typical output); the float-accumulation bar of the benchmark
     # configuration, 1e-4 with the reference's rule |e - a| <= tol * max(1, |e|), holds as well
     assert orc.close(ref[0], y, 1e-4), f"max err {orc.max_err(ref[0], y):.3e}"
+
+
+@pytest.mark.parametrize("M,Nn,K", [(700, 264, 1040), (1024, 768, 2048), (257, 520, 4096), (900, 1000, 256)])
+@pytest.mark.parametrize("epi", [N.EPI_BIAS, N.EPI_BIAS_RESIDUAL])
+def test_cta_pair_kernel_with_k_blocks_dealt_out_evenly(dev, orc, M, Nn, K, epi):
+    """When the last wave of 256 x 256 tiles would leave many clusters idle (2048 x 4096: 128 tiles on 74 clusters), the
+    pair kernel deals the tiles' k-blocks out in equal shares, and a tile that straddles two clusters is completed
+    through a work area (its last k-blocks are computed first by one cluster, its first k-blocks last by the other,
+    which adds the two exact int32 parts).  Forced here on shapes the oracle can check in full: bit-exact accumulators
+    and outputs, twice in a row (the arrival counts of the work area are cleared per launch)."""
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=17)
+    res = orc.normal((M, Nn), 79) if epi == N.EPI_BIAS_RESIDUAL else None
+    acc = orc.qmatmul_i8_acc(aq, wq)
+    exp = orc.dequant_epilogue(acc, a_s, w_s, bias, residual=res)
+    dev.tune(512, 2)
+    try:
+        for rep in range(2):
+            y, raw = _run(dev, aq, a_s, wq, w_s, bias, residual=res, epilogue=epi)
+            assert np.array_equal(raw, acc), f"repetition {rep}: accumulators differ at {np.argwhere(raw != acc)[:4]}"
+            assert np.array_equal(y.view(np.uint32), exp.view(np.uint32)), f"repetition {rep}"
+        yb, _ = _run(dev, aq, a_s, wq, w_s, bias, residual=res, epilogue=epi, out_dtype=N.NS_BF16, want_raw=False)
+    finally:
+        dev.tune(0, 0)
+    assert np.array_equal(yb, orc.round_bf16(exp))
