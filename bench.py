@@ -48,7 +48,7 @@ CONFIG = {"workload": "int8 QuantizedMatMul M=8192 K=4096 N=4096 (per-row A scal
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture summarised
 # in profiles/.
-TRAFFIC_BYTES_PER_LAUNCH = 149024512  # 63.85 MB read + 85.18 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
+TRAFFIC_BYTES_PER_LAUNCH = 146382848  # 61.31 MB read + 85.08 MB write, profiles/qmatmul_i8_m8192_k4096_n4096.md
 
 
 def measured_peaks():
@@ -435,13 +435,13 @@ def run_ours(args, rank, world, local_rank):
         step(i)
     dev.record(e1)
     est_ms = max(dev.elapsed_ms(e0, e1) / 20, 1e-3)
-    executed = max(args.steps, int(MIN_TIMED_SECONDS * 1e3 / est_ms) + 1)
+    executed = args.steps if args.short else max(args.steps, int(MIN_TIMED_SECONDS * 1e3 / est_ms) + 1)
     executed = int(max_over_ranks(float(executed)))
     sampler = ClockSampler(local_rank)
     dev.synchronize()
     if rank == 0:
         sampler.start()
-    load_for(0.45)
+    load_for(0.0 if args.short else 0.45)
     barrier()
     dev.record(e0)
     for i in range(executed):
@@ -449,7 +449,7 @@ def run_ours(args, rank, world, local_rank):
     dev.record(e1)
     ms_total = dev.elapsed_ms(e0, e1)
     barrier()
-    load_for(0.45)
+    load_for(0.0 if args.short else 0.45)
     clocks = sampler.stop() if rank == 0 else None
     ms_total = max_over_ranks(ms_total)
     ms_step = ms_total / executed
@@ -463,7 +463,7 @@ def run_ours(args, rank, world, local_rank):
     N.call("ns_fill_normal", dev.handle, pw.ptr, N.NS_I8, C.c_int64(NN * KP), 22, 0.0, 40.0)
     for _ in range(3):
         N.call("ns_bench_i8_mainloop", dev.handle, pa.ptr, pw.ptr, M, NN, KP)
-    n_proxy = 200
+    n_proxy = 3 if args.short else 200
     barrier()
     dev.record(e0)
     for _ in range(n_proxy):
@@ -802,6 +802,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-gpt", action="store_true", help="skip the decoder's generation (the int8 product line only)")
+    ap.add_argument("--short", action="store_true", help="for launch lists under a profiler: exactly --steps timed steps, no loaded phases around "
+                                                         "them, no main-loop yardstick (the numbers printed are then not benchmark values)")
     ap.add_argument("--no-tp1", action="store_true", help="several GPUs: skip the one-GPU run the tokens are compared with")
     ap.add_argument("--gpt-layers", type=int, default=GPT["layers"])
     ap.add_argument("--gpt-tokens", type=int, default=GPT["new_tokens"])
