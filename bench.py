@@ -192,7 +192,7 @@ def decode_step_bytes(cfg, batch: int, context: float, gpus: int) -> float:
 
 
 def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tokens: int, compare_tp1: bool, fused: int | None = None,
-                   attn_quant: bool | None = None, batch: int | None = None):
+                   attn_quant: bool | None = None, batch: int | None = None, unfused_rows: int | None = None):
     """Builds the decoder tensor-parallel over the ranks of the run, warms up, times one generation; returns the
     `gpt_decode` record on rank 0 (None elsewhere)."""
     from nn_b200 import dist as nsdist
@@ -212,6 +212,8 @@ def run_gpt_decode(dev, rank: int, world: int, peaks: dict, layers: int, new_tok
         model.fused = fused
     if attn_quant is not None:
         model.attn_quant = attn_quant
+    if unfused_rows is not None:
+        model.unfused_rows = unfused_rows
     if world > 1:
         # the prompt is read by batch sharding (a full copy of the weights per GPU), decoding is tensor-parallel
         model.enable_batch_sharded_prefill(weights)
@@ -583,12 +585,13 @@ def run_case(spec: str):
                               beyond L2, beside the same graph of an empty kernel: prints time, GB/s and fraction of the HBM peak
       attention_decode:L      batch 64, 32 heads, head_dim 128, cache length L
       attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
-      gpt_decode:LAYERS[:T[:F[:Q[:B]]]] the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64,
+      gpt_decode:LAYERS[:T[:F[:Q[:B[:U]]]]] the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64,
                               prompt 512) cut to LAYERS layers, T new tokens (default 64): prints the gpt_decode record
                               of the default run.  Under `python -m torch.distributed.run --nproc-per-node N` the decoder
                               is tensor-parallel over N GPUs (one rank per GPU, the slowest rank's times are printed by rank 0).
                               F picks the few-row pass: 2 one launch per Linear, 1 product + fused row kernel, 0 one kernel per operator;
-                              Q = 0 keeps the row quantisation after attention a kernel of its own; B = batch instead of 64
+                              Q = 0 keeps the row quantisation after attention a kernel of its own; B = batch instead of 64; U = passes of up to U
+                              rows take one kernel per operator
     """
     from nn_b200 import native as N
     from nn_b200.device import Device
@@ -780,11 +783,11 @@ def run_case(spec: str):
             N.call("ns_attention_prefill", dev.handle, q.ptr, k.ptr, v.ptr, o.ptr, B, H, S, 128, st, st, st, st, C.c_float(0.0884), 1)
     elif name == "gpt_decode":
         from nn_b200 import dist as nsdist
-        parts = arg.split(":") + ["", "", "", "", ""]
+        parts = arg.split(":") + ["", "", "", "", "", ""]
         rank, world, _ = nsdist.env_rank()
         rec = run_gpt_decode(dev, rank, world, measured_peaks(), int(parts[0] or 2), int(parts[1] or 64), compare_tp1=False,
                              fused=int(parts[2]) if parts[2] else None, attn_quant=bool(int(parts[3])) if parts[3] else None,
-                             batch=int(parts[4]) if parts[4] else None)
+                             batch=int(parts[4]) if parts[4] else None, unfused_rows=int(parts[5]) if parts[5] else None)
         if rank == 0:
             print(json.dumps({"case": spec, "ok": True, "gpt_decode": rec}))
         return

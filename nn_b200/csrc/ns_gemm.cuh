@@ -56,6 +56,9 @@ constexpr int NS_TAIL_MAX_ROWS = 256;
 // fields, out / raw and the scale, bias and residual pointers.
 bool ns_gemv_i8_fits(int M, int K);
 int ns_gemv_i8_run(NsDevice* d, const NsGemmParams& p, const void* a, const void* w);
+// The streaming int8 kernel for 9..64 activation rows (ns_stream_i8.cu): one launch, K summed inside the CTA.  Same fields of `p`.
+bool ns_stream_i8_fits(int M, int K);
+int ns_stream_i8_run(NsDevice* d, const NsGemmParams& p, const void* a, const void* w);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ float ns_gemm_residual(const NsGemmParams& p, size_t idx)

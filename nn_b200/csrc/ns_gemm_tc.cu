@@ -1060,6 +1060,13 @@ int ns_gemm_run(NsDevice* d, int kind, const void* a, const void* b, bool b_is_k
     if (kind == NS_KIND_I8 && !deferred && tail == nullptr && d->force_bn == 0 && d->force_splits == 0 && ns_gemv_i8_fits(M, K) &&
         ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0)
         return ns_gemv_i8_run(d, p, a, b);
+    // Nine to sixteen rows whose K fits the registers of one CTA: the streaming kernel (weights straight into registers,
+    // mma.sync, K summed inside the CTA, epilogue in the same launch).  NS_B200_STREAM=0 keeps the tcgen05 kernels.
+    static int stream_env = -1;
+    if (stream_env < 0) { const char* e = getenv("NS_B200_STREAM"); stream_env = (e != nullptr && e[0] == '0') ? 0 : 1; }
+    if (stream_env == 1 && kind == NS_KIND_I8 && !deferred && tail == nullptr && d->force_bn == 0 && d->force_splits == 0 && ns_stream_i8_fits(M, K) &&
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0)
+        return ns_stream_i8_run(d, p, a, b);
     p.k_blocks = (int)(((int64_t)K * elsize + BKB - 1) / BKB);
     int bn, splits;
     ns_gemm_choose_tiling(d, M, N, p.k_blocks, &bn, &splits, b_is_kn);

@@ -62,13 +62,13 @@ extern "C" int ns_qmatmul_i8_static(ns_device_t h, uint64_t aq, uint64_t a_scale
     NS_REQUIRE(M > 0 && N > 0 && K > 0, NS_ERR_ARGUMENT, "ns_qmatmul_i8_static: empty dimension");
     // size check first, so that an oversized request fails before anything is queued
     // (the split count the launcher ends up with: the requested count shrinks when the k-blocks do not divide evenly;
-    // one to eight rows take the row-streaming kernel, which has no partial sums)
+    // one to eight rows take the row-streaming kernel and nine to sixteen the streaming kernel, which have no partial sums)
     int tile_n = 0, splits = 1;
     const int k_blocks = (K + 127) / 128;
     ns_gemm_choose_tiling(d, M, N, k_blocks, &tile_n, &splits);
     const int kb_per_split = (k_blocks + splits - 1) / splits;
     splits = (k_blocks + kb_per_split - 1) / kb_per_split;
-    const bool streams_rows = d->force_bn == 0 && d->force_splits == 0 && ns_gemv_i8_fits(M, K) && ((aq | wq) & 15) == 0;
+    const bool streams_rows = d->force_bn == 0 && d->force_splits == 0 && (ns_gemv_i8_fits(M, K) || ns_stream_i8_fits(M, K)) && ((aq | wq) & 15) == 0;
     const size_t need = (splits > 1 && !streams_rows) ? (size_t)splits * M * N * 4 : 0;
     NS_REQUIRE(need <= NS_STATIC_SCRATCH_BYTES, NS_ERR_MEMORY,
                "ns_qmatmul_i8_static: M=%d N=%d K=%d splits K %d ways and needs %zu bytes of partial sums; the fixed scratch array holds %u",

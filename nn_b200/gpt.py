@@ -165,6 +165,9 @@ class GptW8A8:
         # overlaps the row kernel), 2 = one launch per Linear (the row operator runs as the product kernel's second phase;
         # fewer launches, measured slower), 0 / False = one kernel per operator
         self.fused = 1
+        # passes of up to this many rows take one kernel per operator instead (their products are one-launch streaming
+        # kernels with the epilogue inside)
+        self.unfused_rows = GEMV_MAX_ROWS
         # True: decode attention quantises its output rows itself (ns_attention_decode_quant: one launch less per layer).
         # Measured on the 24-layer model, batch 64: 2.49 ms per step against 2.44 with the row kernel of its own (the last
         # CTA of a row works alone while the others have left), so it stays off.
@@ -199,7 +202,7 @@ class GptW8A8:
             return self._forward_one_launch(steps)
         # (one to eight rows: the products are row-streaming kernels with their epilogues inside, one launch each, and the
         # pass with one kernel per operator is the faster one -- 1.32 against 1.38 ms per step at batch 8)
-        if self.tp == 1 and GEMV_MAX_ROWS < m <= FUSED_MAX_ROWS and self.fused:
+        if self.tp == 1 and self.unfused_rows < m <= FUSED_MAX_ROWS and self.fused:
             return self._forward_fused(steps)
         if self.tp > 1 and m <= FUSED_MAX_ROWS and self.fused and self.peer is not None:
             return self._forward_tp_fused(steps)

@@ -233,3 +233,38 @@ def test_cta_pair_kernel_with_k_blocks_dealt_out_evenly(dev, orc, M, Nn, K, epi)
     finally:
         dev.tune(0, 0)
     assert np.array_equal(yb, orc.round_bf16(exp))
+
+
+@pytest.mark.parametrize("M,Nn,K", [(9, 40, 64), (16, 4096, 4096), (16, 1001, 8192), (13, 132, 144), (12, 6, 1040), (16, 2048, 2048), (10, 520, 2048),
+                                    (16, 777, 1024), (11, 64, 4096), (16, 6144, 2048), (16, 3, 16), (15, 1000, 1040), (16, 32000, 256)])
+def test_streaming_kernel_for_9_to_16_rows_bit_exact(dev, orc, M, Nn, K):
+    """Nine to sixteen rows take the one-launch streaming kernel (weights straight into registers, mma.sync.m16n8k32, K
+    summed inside the CTA): every register shape (1, 2, 4, 8 K groups per warp), ragged K groups, columns that are no
+    multiple of 8, fewer column tiles than CTAs.  Accumulators and every epilogue equal the oracle's and the tcgen05
+    kernels' (forced by the tuning hook) bit for bit."""
+    aq, a_s, wq, w_s, bias = _inputs(orc, M, Nn, K, seed=23)
+    res = orc.normal((M, Nn), 80)
+    acc = orc.qmatmul_i8_acc(aq, wq)
+    y, raw = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS)
+    assert np.array_equal(raw, acc), f"accumulators differ at {np.argwhere(raw != acc)[:4]}"
+    exp = orc.dequant_epilogue(acc, a_s, w_s, bias)
+    assert np.array_equal(y.view(np.uint32), exp.view(np.uint32))
+    y, _ = _run(dev, aq, a_s, wq, w_s, None, epilogue=N.EPI_NONE, want_raw=False)
+    assert np.array_equal(y.view(np.uint32), orc.dequant_epilogue(acc, a_s, w_s).view(np.uint32))
+    res_b = orc.round_bf16(res)
+    yb, _ = _run(dev, aq, a_s, wq, w_s, bias, residual=res_b, epilogue=N.EPI_BIAS_RESIDUAL, out_dtype=N.NS_BF16, residual_dtype=N.NS_BF16,
+                 want_raw=False)
+    assert np.array_equal(yb, orc.round_bf16(orc.dequant_epilogue(acc, a_s, w_s, bias, residual=orc.widen_bf16(res_b))))
+    y, _ = _run(dev, aq, a_s, wq, w_s, bias, residual=res, epilogue=N.EPI_BIAS_RESIDUAL, want_raw=False)
+    assert np.array_equal(y.view(np.uint32), orc.dequant_epilogue(acc, a_s, w_s, bias, residual=res).view(np.uint32))
+    yg, _ = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS_GELU, want_raw=False)
+    assert orc.close(orc.dequant_epilogue(acc, a_s, w_s, bias, act=1), yg, 1e-5)
+    dev.tune(64, 2 if K >= 512 else 1)
+    try:
+        y_tc, raw_tc = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS)
+        yg_tc, _ = _run(dev, aq, a_s, wq, w_s, bias, epilogue=N.EPI_BIAS_GELU, want_raw=False)
+    finally:
+        dev.tune(0, 0)
+    assert np.array_equal(raw_tc, acc)
+    assert np.array_equal(y_tc.view(np.uint32), exp.view(np.uint32))
+    assert np.array_equal(yg_tc.view(np.uint32), yg.view(np.uint32)), "GELU epilogue differs between the two kernels"
