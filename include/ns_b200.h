@@ -130,6 +130,9 @@ NS_API int ns_graph_destroy(ns_graph_t graph);
 NS_API int ns_event_create(ns_device_t dev, uint64_t* event);
 NS_API int ns_event_record(ns_device_t dev, uint64_t event);
 NS_API int ns_event_elapsed_ms(ns_device_t dev, uint64_t start, uint64_t stop, float* ms);  /* waits for `stop` */
+/* Work queued on dev's stream after this call waits for `event`, which may have been recorded on another device object of
+ * the same GPU (cuStreamWaitEvent; the reference has one stream per device and no counterpart). */
+NS_API int ns_stream_wait_event(ns_device_t dev, uint64_t event);
 NS_API int ns_event_destroy(ns_device_t dev, uint64_t event);
 
 /* ------------------------------------------------------------------------------------------------

@@ -511,6 +511,18 @@ extern "C" int ns_event_record(ns_device_t h, uint64_t event)
     return NS_OK;
 }
 
+// Work queued on `dev`'s stream after this call waits for `event` (recorded on any stream of the same GPU, for instance
+// another device object's): how two device objects of one GPU order a hand-over without a host synchronisation.
+extern "C" int ns_stream_wait_event(ns_device_t h, uint64_t event)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(event != 0, NS_ERR_ARGUMENT, "ns_stream_wait_event: event is null");
+    NS_CUDA(cudaStreamWaitEvent(d->stream, reinterpret_cast<cudaEvent_t>(event), 0));
+    return NS_OK;
+}
+
 extern "C" int ns_event_elapsed_ms(ns_device_t h, uint64_t start, uint64_t stop, float* ms)
 {
     NsDevice* d = ns_dev(h);

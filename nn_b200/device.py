@@ -120,6 +120,10 @@ class Device:
     def record(self, event: int) -> None:
         N.call("ns_event_record", self.handle, C.c_uint64(event))
 
+    def wait_event(self, event: int) -> None:
+        """Work queued on this device object's stream from now on waits for `event` (recorded on any stream of the GPU)."""
+        N.call("ns_stream_wait_event", self.handle, C.c_uint64(event))
+
     def elapsed_ms(self, start: int, stop: int) -> float:
         ms = C.c_float()
         N.call("ns_event_elapsed_ms", self.handle, C.c_uint64(start), C.c_uint64(stop), C.byref(ms))

@@ -129,6 +129,7 @@ class GptW8A8:
             N.call("ns_kv_cache_create_in", dev.handle, batch * self.max_pages, page_size, self.heads_loc, cfg.head_dim,
                    C.c_uint64(self.kv_block.ptr + 2 * i * self.pool_bytes), C.c_uint64(self.kv_block.ptr + (2 * i + 1) * self.pool_bytes), C.byref(h))
             self.caches.append(h)
+        self.after_kv_append = None    # callback(layer) of the many-row pass, right after a layer's keys / values are in the cache
         self.replica = None            # a one-GPU model of batch / tp sequences for the batch-sharded prompt read
         self._peer_kv = None           # every rank's kv_block as mapped here
         self._bar = None
@@ -211,11 +212,13 @@ class GptW8A8:
                N.NS_BF16, x_in.ptr)
         self._n += 1
         whole_sequence = steps > 1 and self.length == 0 and dh == 128
-        for L, cache in zip(self.layers, self.caches):
+        for li, (L, cache) in enumerate(zip(self.layers, self.caches)):
             N.call("ns_layernorm", h, x_in.ptr, N.NS_BF16, L["ln1"][0].ptr, L["ln1"][1].ptr, C.c_int64(m), D, eps, N.NS_I8, self.hq.ptr, self.hq_scale.ptr)
             L["qkv"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS, N.NS_BF16, self.qkv.ptr)
             q, k, v = self.qkv.ptr, self.qkv.ptr + 2 * dl, self.qkv.ptr + 4 * dl
             N.call("ns_kv_append", h, cache, C.c_uint64(k), C.c_uint64(v), C.c_int64(3 * dl), self.page_table.ptr, self.max_pages, self.pos.ptr, B, steps)
+            if self.after_kv_append is not None:
+                self.after_kv_append(li)
             if whole_sequence:
                 st_in = (C.c_int64 * 3)(steps * 3 * dl, dh, 3 * dl)
                 st_out = (C.c_int64 * 3)(steps * dl, dh, dl)
@@ -479,6 +482,12 @@ class GptW8A8:
         self.replica = GptW8A8(self.dev, self.cfg, weights, self.batch // self.tp, self.max_rows // self.batch, page_size=self.page_size)
         mine = C.create_string_buffer(64)
         N.call("ns_ipc_handle", self.dev.handle, C.c_uint64(self.kv_block.ptr), mine)
+        # a second device object on the same GPU: its stream carries the key/value delivery of layer l while the prompt read
+        # works on layer l + 1
+        from .device import Device
+        self._side = Device(self.dev.ordinal)
+        self._kv_events = [self.dev.event() for _ in range(self.cfg.layers)]
+        self._side_done = self.dev.event()
         self._peer_kv = []
         for r, handle in enumerate(dist.all_gather_bytes(mine.raw)):
             if r == self.rank:
@@ -497,15 +506,39 @@ class GptW8A8:
         if self._bar is None:
             self._bar = self.dev.zeros(8, N.NS_I32)
         N.call("ns_allreduce", h, self.comm, C.c_uint64(self._bar.ptr), C.c_int64(1), N.NS_I32)
-        rep.prefill(ids[self.rank * bl:(self.rank + 1) * bl])
         pages_used = (t + self.page_size - 1) // self.page_size
-        # one launch for all layers: both models keep [layer][keys, values] pools in one allocation
         arr = C.c_uint64 * self.tp
-        dk = arr(*self._peer_kv)
-        dv = arr(*[p + self.pool_bytes for p in self._peer_kv])
-        N.call("ns_kv_scatter_heads", h, rep.caches[0], rep.page_table.ptr, rep.max_pages, bl, self.rank * bl, pages_used, dk, dv, self.tp, self.heads_loc,
-               self.batch * self.max_pages, self.page_table.ptr, self.max_pages, self.cfg.layers, C.c_uint64(2 * rep.pool_bytes),
-               C.c_uint64(2 * self.pool_bytes))
+        side = self._side
+        if bl * t > FUSED_MAX_ROWS:
+            # The delivery of layer l runs on the side stream while the read computes layer l + 1: the side stream first
+            # waits for the barrier above (an event on the main stream), then per layer for that layer's keys / values.
+            self.dev.record(self._side_done)
+            side.wait_event(self._side_done)
+
+            def deliver(layer: int) -> None:
+                self.dev.record(self._kv_events[layer])
+                side.wait_event(self._kv_events[layer])
+                dk = arr(*[p + 2 * layer * self.pool_bytes for p in self._peer_kv])
+                dv = arr(*[p + (2 * layer + 1) * self.pool_bytes for p in self._peer_kv])
+                N.call("ns_kv_scatter_heads", side.handle, rep.caches[layer], rep.page_table.ptr, rep.max_pages, bl, self.rank * bl, pages_used, dk, dv,
+                       self.tp, self.heads_loc, self.batch * self.max_pages, self.page_table.ptr, self.max_pages, 1, C.c_uint64(0), C.c_uint64(0))
+
+            rep.after_kv_append = deliver
+            try:
+                rep.prefill(ids[self.rank * bl:(self.rank + 1) * bl])
+            finally:
+                rep.after_kv_append = None
+            side.record(self._side_done)
+            self.dev.wait_event(self._side_done)
+        else:
+            # a short re-read goes through the few-row pass: deliver all layers afterwards, in one launch (both models keep
+            # [layer][keys, values] pools in one allocation)
+            rep.prefill(ids[self.rank * bl:(self.rank + 1) * bl])
+            dk = arr(*self._peer_kv)
+            dv = arr(*[p + self.pool_bytes for p in self._peer_kv])
+            N.call("ns_kv_scatter_heads", h, rep.caches[0], rep.page_table.ptr, rep.max_pages, bl, self.rank * bl, pages_used, dk, dv, self.tp,
+                   self.heads_loc, self.batch * self.max_pages, self.page_table.ptr, self.max_pages, self.cfg.layers, C.c_uint64(2 * rep.pool_bytes),
+                   C.c_uint64(2 * self.pool_bytes))
         # the first tokens of all sequences; a rank's share leaves only after its stores above are complete (stream order), and
         # the gather completes only when every rank has contributed: after it, every cache holds every sequence's prompt
         N.call("ns_allgather", h, self.comm, C.c_uint64(rep.ids.ptr), C.c_uint64(self.ids.ptr), C.c_int64(bl), N.NS_I32)
@@ -661,6 +694,8 @@ class GptW8A8:
         if self.replica is not None:
             self.replica.close()
             self.replica = None
+            self._side.synchronize()
+            self._side.close()
         for c in self.caches:
             N.call("ns_kv_cache_destroy", c)
         self.caches = []

@@ -54,6 +54,7 @@ SIGNATURES = {
     "ns_event_record": [vp, u64],
     "ns_event_elapsed_ms": [vp, u64, u64, P(f32)],
     "ns_event_destroy": [vp, u64],
+    "ns_stream_wait_event": [vp, u64],
     "ns_quantize_rows_i8": [vp, u64, i32, i64, i32, u64, u64],
     "ns_qmatmul_i8": [vp, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, u64, u64],
     "ns_qmatmul_i8_static": [vp, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, u64],

@@ -92,34 +92,41 @@ def gpu_mode():
     m2.close()
     # ---- prompt read by batch sharding, keys / values delivered into the head-sharded caches over peer memory: the pages
     # this rank ends up with must equal, bit for bit, the pages of its heads in a ONE-GPU model's cache (which is what
-    # every rank computed for its share of the sequences), the first tokens likewise; decoding then goes on tensor-parallel
-    B4 = 2 * world
-    prompt4 = orc.token_ids((B4, 12), 45, cfg.vocab).astype(np.int32)
-    one = GptW8A8(dev, cfg, w, B4, max_prefill=16)
-    one.prefill(prompt4)
-    dev.synchronize()
-    one_pools = one.kv_block.download().view(np.uint16).reshape(cfg.layers, 2, B4 * one.max_pages, cfg.heads, one.page_size, cfg.head_dim)
-    one_ids, one_logits = one.read_ids().copy(), one.read_logits().copy()
-    m3 = GptW8A8(dev, cfg, w, B4, max_prefill=16, tp_rank=rank, tp_size=world, comm=comm)
-    m3.enable_batch_sharded_prefill(w)
-    m3.prefill(prompt4)
-    dev.synchronize()
-    dist.barrier()
-    mine3 = m3.kv_block.download().view(np.uint16).reshape(cfg.layers, 2, B4 * m3.max_pages, m3.heads_loc, m3.page_size, cfg.head_dim)
-    hl = m3.heads_loc
-    assert np.array_equal(mine3, one_pools[:, :, :, rank * hl:(rank + 1) * hl]), "delivered keys / values differ from the one-GPU cache"
-    assert mine3.any()
-    assert np.array_equal(m3.read_ids(), one_ids), "gathered first tokens differ from the one-GPU model's"
-    bl = B4 // world
-    assert np.array_equal(m3.replica.read_logits().view(np.uint32), one_logits[rank * bl:(rank + 1) * bl].view(np.uint32))
-    got3, _ = m3.generate(prompt4, 10, use_graph=True)
-    mine = torch.from_numpy(got3.astype(np.int64))
-    ref0 = mine.clone()
-    td.broadcast(ref0, 0)
-    assert torch.equal(mine, ref0), "ranks disagree on the tokens after a batch-sharded prompt read"
-    assert np.array_equal(got3[:, 0], one_ids)
-    m3.close()
-    one.close()
+    # every rank computed for its share of the sequences), the first tokens likewise; decoding then goes on tensor-parallel.
+    # Twice: a short prompt (few rows: all layers delivered in one launch after the read) and a long one (many rows: layer
+    # l delivered on a side stream while the read works on layer l + 1).
+    import torch
+    import torch.distributed as td
+    for context, prompt_len in ((32, 12), (320, 160)):
+        cfg2 = GptConfig(vocab=cfg.vocab, dim=cfg.dim, heads=cfg.heads, layers=cfg.layers, ff_dim=cfg.ff_dim, context=context)
+        w2 = om.make_weights(cfg2, seed=4)
+        B4 = 2 * world
+        prompt4 = orc.token_ids((B4, prompt_len), 45, cfg2.vocab).astype(np.int32)
+        one = GptW8A8(dev, cfg2, w2, B4, max_prefill=prompt_len + 4)
+        one.prefill(prompt4)
+        dev.synchronize()
+        one_pools = one.kv_block.download().view(np.uint16).reshape(cfg2.layers, 2, B4 * one.max_pages, cfg2.heads, one.page_size, cfg2.head_dim)
+        one_ids, one_logits = one.read_ids().copy(), one.read_logits().copy()
+        m3 = GptW8A8(dev, cfg2, w2, B4, max_prefill=prompt_len + 4, tp_rank=rank, tp_size=world, comm=comm)
+        m3.enable_batch_sharded_prefill(w2)
+        m3.prefill(prompt4)
+        dev.synchronize()
+        dist.barrier()
+        mine3 = m3.kv_block.download().view(np.uint16).reshape(cfg2.layers, 2, B4 * m3.max_pages, m3.heads_loc, m3.page_size, cfg2.head_dim)
+        hl = m3.heads_loc
+        assert np.array_equal(mine3, one_pools[:, :, :, rank * hl:(rank + 1) * hl]), "delivered keys / values differ from the one-GPU cache"
+        assert mine3.any()
+        assert np.array_equal(m3.read_ids(), one_ids), "gathered first tokens differ from the one-GPU model's"
+        bl = B4 // world
+        assert np.array_equal(m3.replica.read_logits().view(np.uint32), one_logits[rank * bl:(rank + 1) * bl].view(np.uint32))
+        got3, _ = m3.generate(prompt4, 10, use_graph=True)
+        mine = torch.from_numpy(got3.astype(np.int64))
+        ref0 = mine.clone()
+        td.broadcast(ref0, 0)
+        assert torch.equal(mine, ref0), "ranks disagree on the tokens after a batch-sharded prompt read"
+        assert np.array_equal(got3[:, 0], one_ids)
+        m3.close()
+        one.close()
     dist.barrier()
     print(f"rank {rank}: gpu ok, agreement {agree:.3f}")
 
