@@ -585,6 +585,8 @@ def run_case(spec: str):
                               beyond L2, beside the same graph of an empty kernel: prints time, GB/s and fraction of the HBM peak
       attention_decode:L      batch 64, 32 heads, head_dim 128, cache length L
       attention_prefill:S     batch 8, 32 heads, head_dim 128, sequence S, causal
+      prefill_parts           one decoder layer of the prompt read of benchmark configuration 5 (32768 rows), operator by operator: time,
+                              bytes and GB/s (row kernels) or TOPS (products, attention) of each
       gpt_decode:LAYERS[:T[:F[:Q[:B[:U]]]]] the int8 decoder of benchmark configuration 5 (d 2048, 16 heads, ff 8192, vocabulary 32000, batch 64,
                               prompt 512) cut to LAYERS layers, T new tokens (default 64): prints the gpt_decode record
                               of the default run.  Under `python -m torch.distributed.run --nproc-per-node N` the decoder
@@ -781,6 +783,63 @@ def run_case(spec: str):
         st = (C.c_int64 * 3)(H * S * 128, S * 128, 128)
         for _ in range(3):
             N.call("ns_attention_prefill", dev.handle, q.ptr, k.ptr, v.ptr, o.ptr, B, H, S, 128, st, st, st, st, C.c_float(0.0884), 1)
+    elif name == "prefill_parts":
+        # One decoder layer of the prompt read (batch 64 x 512 positions = 32768 rows, d 2048, 16 heads, ff 8192), operator by
+        # operator, each timed alone over 10 launches: where a layer's time goes, and what rate each row kernel reaches.
+        from nn_b200.gpt import GptConfig, GptW8A8
+        peaks = measured_peaks()
+        g = GPT
+        B, S = g["batch"], g["prompt"]
+        cfg = GptConfig(vocab=g["vocab"], dim=g["dim"], heads=g["heads"], layers=1, ff_dim=g["ff_dim"], context=S + 8)
+        model = GptW8A8(dev, cfg, SyntheticGptWeights(cfg, g["seed"]), B, max_prefill=S)
+        model.prefill(gpt_prompt(cfg, B, S, g["seed"]))       # fills every buffer with real activations
+        dev.synchronize()
+        h, D, FF, dh, m = dev.handle, cfg.dim, cfg.ff_dim, cfg.head_dim, B * S
+        L, cache = model.layers[0], model.caches[0]
+        x_in, x_out = model.x
+        eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
+        q, k, v = model.qkv.ptr, model.qkv.ptr + 2 * D, model.qkv.ptr + 4 * D
+        st_in, st_out = (C.c_int64 * 3)(S * 3 * D, dh, 3 * D), (C.c_int64 * 3)(S * D, dh, D)
+        zero_pos = dev.zeros(B, N.NS_I32)
+        ops = [
+            ("layernorm -> int8 [m, 2048]", 3 * m * D, 0,
+             lambda: N.call("ns_layernorm", h, x_in.ptr, N.NS_BF16, L["ln1"][0].ptr, L["ln1"][1].ptr, C.c_int64(m), D, eps, N.NS_I8, model.hq.ptr, model.hq_scale.ptr)),
+            ("qkv product [m, 2048] x [2048, 6144]", m * D + 6 * m * D, 2 * m * D * 3 * D,
+             lambda: L["qkv"].forward(model.hq.ptr, model.hq_scale.ptr, m, N.EPI_BIAS, N.NS_BF16, model.qkv.ptr)),
+            ("key / value append", 8 * m * D, 0,
+             lambda: N.call("ns_kv_append", h, cache, C.c_uint64(k), C.c_uint64(v), C.c_int64(3 * D), model.page_table.ptr, model.max_pages, zero_pos.ptr, B, S)),
+            ("causal attention", 8 * m * D, 2 * 2 * B * cfg.heads * S * S * dh // 2,
+             lambda: N.call("ns_attention_prefill", h, C.c_uint64(q), C.c_uint64(k), C.c_uint64(v), model.attn.ptr, B, cfg.heads, S, dh, st_in, st_in, st_in, st_out, scale, 1)),
+            ("quantise [m, 2048]", 3 * m * D, 0,
+             lambda: N.call("ns_quantize_rows_i8", h, model.attn.ptr, N.NS_BF16, C.c_int64(m), D, model.hq.ptr, model.hq_scale.ptr)),
+            ("output product + residual [m, 2048] x [2048, 2048]", m * D + 4 * m * D, 2 * m * D * D,
+             lambda: L["out"].forward(model.hq.ptr, model.hq_scale.ptr, m, N.EPI_BIAS_RESIDUAL, N.NS_BF16, x_out.ptr, residual=x_in.ptr)),
+            ("ff1 product + GELU [m, 2048] x [2048, 8192]", m * D + 2 * m * FF, 2 * m * D * FF,
+             lambda: L["ff1"].forward(model.hq.ptr, model.hq_scale.ptr, m, N.EPI_BIAS_GELU, N.NS_BF16, model.ffh.ptr)),
+            ("quantise [m, 8192]", 3 * m * FF, 0,
+             lambda: N.call("ns_quantize_rows_i8", h, model.ffh.ptr, N.NS_BF16, C.c_int64(m), FF, model.hq.ptr, model.hq_scale.ptr)),
+            ("ff2 product + residual [m, 8192] x [8192, 2048]", m * FF + 4 * m * D, 2 * m * D * FF,
+             lambda: L["ff2"].forward(model.hq.ptr, model.hq_scale.ptr, m, N.EPI_BIAS_RESIDUAL, N.NS_BF16, x_out.ptr, residual=x_in.ptr)),
+        ]
+        e0, e1 = dev.event(), dev.event()
+        rows, total = [], 0.0
+        for label, nbytes, nops, fn in ops:
+            for _ in range(3):
+                fn()
+            dev.synchronize()
+            dev.record(e0)
+            for _ in range(10):
+                fn()
+            dev.record(e1)
+            dev.synchronize()
+            us = dev.elapsed_ms(e0, e1) * 100.0
+            total += us
+            gbs = nbytes / (us * 1e-6) / 1e9
+            rows.append({"op": label, "us": us, "bytes": nbytes, "gbs": gbs, "frac_of_hbm": gbs / peaks["hbm"],
+                         "tops": nops / (us * 1e-6) / 1e12 if nops else None})
+        print(json.dumps({"case": spec, "ok": True, "rows": m, "layer_us": total, "hbm_peak_gbs": peaks["hbm"], "ops": rows}))
+        model.close()
+        return
     elif name == "gpt_decode":
         from nn_b200 import dist as nsdist
         parts = arg.split(":") + ["", "", "", "", "", ""]

@@ -74,7 +74,7 @@ __device__ __forceinline__ float ns_gemm_finish_i8(const NsGemmParams& p, int32_
     v = __fmul_rn(v, a_scale);
     v = __fmul_rn(v, w_scale);
     if (p.epilogue != NS_EPI_NONE) v = __fadd_rn(v, bias);
-    if (p.epilogue == NS_EPI_BIAS_GELU) v = ns_gelu_tanh(v);
+    if (p.epilogue == NS_EPI_BIAS_GELU) v = ns_gelu_fast(v);
     return v;
 }
 #endif

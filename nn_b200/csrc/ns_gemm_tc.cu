@@ -75,7 +75,7 @@ __device__ __forceinline__ float finish_value(const NsGemmParams& p, uint32_t bi
     if (KIND == NS_KIND_I8) return ns_gemm_finish_i8(p, static_cast<int32_t>(bits), a_scale, w_scale, bias);
     float v = __uint_as_float(bits);
     if (p.epilogue != NS_EPI_NONE) v = __fadd_rn(v, bias);
-    if (p.epilogue == NS_EPI_BIAS_GELU) v = ns_gelu_tanh(v);
+    if (p.epilogue == NS_EPI_BIAS_GELU) v = ns_gelu_fast(v);
     return v;
 }
 
@@ -113,6 +113,21 @@ __device__ __forceinline__ void add_residual32(const NsGemmParams& p, size_t bas
         for (int j = 0; j < 32; j++)
             if (col0 + j < p.N) v[j] = __fadd_rn(v[j], load_residual(p, base + j));
     }
+}
+
+// While a tile's MMAs are still running its epilogue warps are idle: each lane asks L2 for the part of its row of the
+// residual matrix that the tile's epilogue will add (columns [col_begin, col_end), clipped to the matrix), so that the
+// epilogue's loads, 64 to 128 bytes per lane and chunk at a pitch of a whole row, wait for L2 and not for HBM.
+__device__ __forceinline__ void prefetch_residual_row(const NsGemmParams& p, int row, int col_begin, int col_end)
+{
+    if (p.epilogue != NS_EPI_BIAS_RESIDUAL || p.out == nullptr || p.residual == nullptr || row >= p.M) return;
+    const size_t el = p.residual_dtype == NS_F32 ? 4 : 2;
+    if (col_end > p.N) col_end = p.N;
+    if (col_begin >= col_end) return;
+    const char* base = reinterpret_cast<const char*>(p.residual);
+    const uint64_t first = (reinterpret_cast<uint64_t>(base) + ((size_t)row * p.N + col_begin) * el) & ~uint64_t(127);
+    const uint64_t last = reinterpret_cast<uint64_t>(base) + ((size_t)row * p.N + col_end) * el - 1;
+    for (uint64_t a = first; a <= last; a += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
 }
 
 // Writes this warp's [32 rows x WORDS*4 bytes] block into a staging buffer with the swizzle the
@@ -237,7 +252,7 @@ __device__ __forceinline__ void epilogue_chunk(const NsGemmParams& p, const Stor
         }
         if (p.epilogue == NS_EPI_BIAS_GELU) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = ns_gelu_tanh(v[j]);
+            for (int j = 0; j < 32; j++) v[j] = ns_gelu_fast(v[j]);
         } else if (p.epilogue == NS_EPI_BIAS_RESIDUAL && cx.row_ok) {
             add_residual32(p, base, col0, v);
         }
@@ -452,6 +467,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
                     if (p.epilogue != NS_EPI_NONE) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.bias + pc));
                 }
             }
+            if (p.k_splits == 1) prefetch_residual_row(p, cx.row, tn * BN, tn * BN + BN);
             ok = ns_mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, p.status_base + 4);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -800,6 +816,7 @@ ns_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (p.epilogue != NS_EPI_NONE) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.bias + pc));
                 }
             }
+            if (role != 1) prefetch_residual_row(p, cx.row, tn * BN + c_begin * 32, tn * BN + c_end * 32);
             ok = ns_mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, p.status_base + 14);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;

@@ -167,61 +167,6 @@ __global__ void ns_layernorm_q_reg_kernel(const uint16_t* __restrict__ x, const 
 
 inline unsigned grid_rows(const NsDevice* d, int64_t rows);
 
-// ---- many rows: one warp per row (see ns_rows.cuh); bf16 rows only
-template <int VEC>
-__global__ void __launch_bounds__(256) ns_quantize_rows_warp_kernel(const uint16_t* __restrict__ x, int64_t rows, int8_t* __restrict__ q,
-                                                                      float* __restrict__ scale)
-{
-    ns_pdl_wait();
-    ns_pdl_trigger();
-    constexpr int COLS = VEC * 256;
-    const int lane = threadIdx.x & 31;
-    const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += n_warps) {
-        float v[VEC * 8];
-        const uint16_t* row = x + (size_t)r * COLS;
-#pragma unroll
-        for (int k = 0; k < VEC; k++) {
-            float t[8];
-            ns_rows::widen8(*reinterpret_cast<const uint4*>(row + (k * 32 + lane) * 8), t);
-#pragma unroll
-            for (int i = 0; i < 8; i++) v[k * 8 + i] = t[i];
-        }
-        ns_rows::warp_quantize_row<VEC>(v, q + (size_t)r * COLS, scale + r, lane);
-    }
-}
-
-template <int VEC>
-__global__ void __launch_bounds__(256) ns_layernorm_q_warp_kernel(const uint16_t* __restrict__ x, const float* __restrict__ gamma,
-                                                                    const float* __restrict__ beta, int64_t rows, float eps, int8_t* __restrict__ y,
-                                                                    float* __restrict__ y_scale)
-{
-    ns_pdl_wait();
-    ns_pdl_trigger();
-    constexpr int COLS = VEC * 256;
-    const int lane = threadIdx.x & 31;
-    const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += n_warps) {
-        float v[VEC * 8];
-        const uint16_t* row = x + (size_t)r * COLS;
-#pragma unroll
-        for (int k = 0; k < VEC; k++) {
-            float t[8];
-            ns_rows::widen8(*reinterpret_cast<const uint4*>(row + (k * 32 + lane) * 8), t);
-#pragma unroll
-            for (int i = 0; i < 8; i++) v[k * 8 + i] = t[i];
-        }
-        ns_rows::warp_layernorm_quantize_row<VEC>(v, gamma, beta, eps, y + (size_t)r * COLS, y_scale + r, lane);
-    }
-}
-
-inline unsigned grid_warps(const NsDevice* d, int64_t rows)
-{
-    int64_t blocks = (rows + 7) / 8;
-    const int64_t cap = (int64_t)d->sm_count * 16;
-    return (unsigned)(blocks < cap ? blocks : cap);
-}
-
 template <bool F32IN>
 cudaError_t launch_quantize_reg(NsDevice* d, unsigned threads, int vpt, const void* x, int64_t rows, int cols, int8_t* q, float* scale)
 {
@@ -408,14 +353,8 @@ extern "C" int ns_quantize_rows_i8(ns_device_t h, uint64_t x, int in_dtype, int6
     if (rows == 0) return NS_OK;
     unsigned threads = 0;
     int vpt = 0;
-    if (in_dtype == NS_BF16 && rows >= ns_rows::MANY_ROWS && ((x | q) & 15) == 0 && (cols == 1024 || cols == 2048 || cols == 4096)) {
-        const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
-        int8_t* qp = reinterpret_cast<int8_t*>(q);
-        float* sp = reinterpret_cast<float*>(scale);
-        const dim3 grid(grid_warps(d, rows)), block(256);
-        if (cols == 1024) NS_CUDA(ns_launch_plain(ns_quantize_rows_warp_kernel<4>, grid, block, 0, d->stream, xp, rows, qp, sp));
-        else if (cols == 2048) NS_CUDA(ns_launch_plain(ns_quantize_rows_warp_kernel<8>, grid, block, 0, d->stream, xp, rows, qp, sp));
-        else NS_CUDA(ns_launch_plain(ns_quantize_rows_warp_kernel<16>, grid, block, 0, d->stream, xp, rows, qp, sp));
+    if (in_dtype == NS_BF16 && ((x | q) & 15) == 0 && ns_rows_stream_fits(false, rows, cols)) {
+        NS_CUDA(ns_rows_stream_quantize(d, reinterpret_cast<const uint16_t*>(x), rows, cols, reinterpret_cast<int8_t*>(q), reinterpret_cast<float*>(scale)));
         return NS_OK;
     }
     if (((x | q) & 15) == 0 && ns_rows::row_shape(cols, &threads, &vpt)) {
@@ -443,17 +382,9 @@ extern "C" int ns_layernorm(ns_device_t h, uint64_t x, int in_dtype, uint64_t ga
     if (rows == 0) return NS_OK;
     unsigned threads = 0;
     int vpt = 0;
-    if (in_dtype == NS_BF16 && out_dtype == NS_I8 && rows >= ns_rows::MANY_ROWS && ((x | y | gamma | beta) & 15) == 0 &&
-        (cols == 1024 || cols == 2048 || cols == 4096)) {
-        const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
-        const float* gp = reinterpret_cast<const float*>(gamma);
-        const float* bp = reinterpret_cast<const float*>(beta);
-        int8_t* yp = reinterpret_cast<int8_t*>(y);
-        float* sp = reinterpret_cast<float*>(y_scale);
-        const dim3 grid(grid_warps(d, rows)), block(256);
-        if (cols == 1024) NS_CUDA(ns_launch_plain(ns_layernorm_q_warp_kernel<4>, grid, block, 0, d->stream, xp, gp, bp, rows, eps, yp, sp));
-        else if (cols == 2048) NS_CUDA(ns_launch_plain(ns_layernorm_q_warp_kernel<8>, grid, block, 0, d->stream, xp, gp, bp, rows, eps, yp, sp));
-        else NS_CUDA(ns_launch_plain(ns_layernorm_q_warp_kernel<16>, grid, block, 0, d->stream, xp, gp, bp, rows, eps, yp, sp));
+    if (in_dtype == NS_BF16 && out_dtype == NS_I8 && ((x | y | gamma | beta) & 15) == 0 && ns_rows_stream_fits(true, rows, cols)) {
+        NS_CUDA(ns_rows_stream_layernorm(d, reinterpret_cast<const uint16_t*>(x), reinterpret_cast<const float*>(gamma), reinterpret_cast<const float*>(beta), rows,
+                                         cols, eps, reinterpret_cast<int8_t*>(y), reinterpret_cast<float*>(y_scale)));
         return NS_OK;
     }
     if (in_dtype == NS_BF16 && out_dtype == NS_I8 && ((x | y | gamma | beta) & 15) == 0 && ns_rows::row_shape(cols, &threads, &vpt)) {

@@ -42,6 +42,38 @@ __device__ __forceinline__ int8_t quant_one(float v, float scale)
     return (int8_t)q;
 }
 
+// Eight values -> eight int8 bytes (lo: values 0-3, hi: 4-7), bit for bit what quant_one gives, without eight IEEE
+// divisions.  Precondition: rcp = __frcp_rn(scale), scale = (row maximum) / 127.
+// With u = 2^-15 (a float's ulp in [256, 512)): s_hi = x * rcp + 384.5 + 4u and s_lo = x * rcp + 384.5 - 4u, one fused
+// rounding each.  x * rcp is within 0.25u of the real quotient (|quotient| <= 127.0001), the rounded quotient d the rule
+// asks for within 0.125u, a fused rounding adds 0.5u: d + 384.5 lies in [s_lo + 3u, s_hi - 3u].  So when no integer lies in
+// (s_lo, s_hi] -- the two floors agree -- d + 0.5 is no integer either and floor(s_hi) - 384 is d rounded to nearest,
+// ties included (there is none).  The floors come from an add of 2^23 rounded toward zero, which leaves floor(s) in the low
+// mantissa bits; its low byte is 128 + n, n with its top bit flipped (undone on the packed bytes).  Vectors whose floors
+// differ somewhere (the quotient within 5u of a half-integer: one value in 4000) take the divisions; with FINITE_CHECK so do
+// vectors with a NaN, an infinity or a quotient beyond +-127 in play (the high bits of the floor are then not those of
+// 2^23 + 256..511) -- a caller that has ruled those out for the whole row saves that test.
+template <bool FINITE_CHECK>
+__device__ __forceinline__ void quant8(const float* x, float scale, float rcp, uint32_t& lo, uint32_t& hi)
+{
+    constexpr float U = 1.0f / 32768.0f, OFFSET_HI = 384.5f + 4.0f * U, OFFSET_LO = 384.5f - 4.0f * U, TWO23 = 8388608.0f;
+    uint32_t b[8], differ = 0u, range = 0u;
+#pragma unroll
+    for (int t = 0; t < 8; t++) {
+        const uint32_t n_hi = __float_as_uint(__fadd_rz(fmaf(x[t], rcp, OFFSET_HI), TWO23));
+        const uint32_t n_lo = __float_as_uint(__fadd_rz(fmaf(x[t], rcp, OFFSET_LO), TWO23));
+        differ |= n_hi ^ n_lo;
+        if (FINITE_CHECK) range |= n_hi ^ 0x4B000100u;
+        b[t] = n_hi;
+    }
+    if (differ != 0u || (range & 0xFFFFFF00u) != 0u) {
+#pragma unroll
+        for (int t = 0; t < 8; t++) b[t] = (uint32_t)(uint8_t)quant_one(x[t], scale) ^ 0x80u;
+    }
+    lo = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410) ^ 0x80808080u;
+    hi = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410) ^ 0x80808080u;
+}
+
 // 8 bf16 values (one 16-byte vector) -> 8 floats
 __device__ __forceinline__ void widen8(const uint4 raw, float (&v)[8])
 {
@@ -67,14 +99,11 @@ __device__ __forceinline__ void quantize_row(const float (&x)[VPT * 8], int8_t* 
     amax = block_reduce(amax, true, red);
     const float sc = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
     if (threadIdx.x == 0) *scale_out = sc;
+    const float rcp = __frcp_rn(sc);
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int t = 0; t < 4; t++) {
-            lo |= (uint32_t)(uint8_t)quant_one(x[j * 8 + t], sc) << (8 * t);
-            hi |= (uint32_t)(uint8_t)quant_one(x[j * 8 + 4 + t], sc) << (8 * t);
-        }
+        uint32_t lo, hi;
+        quant8<true>(x + j * 8, sc, rcp, lo, hi);
         *reinterpret_cast<uint2*>(q_row + vec_col(j)) = make_uint2(lo, hi);
     }
 }
@@ -113,10 +142,6 @@ __device__ __forceinline__ void layernorm_quantize_row(float (&x)[VPT * 8], cons
     quantize_row<VPT>(x, q_row, scale_out, sh.red[2]);
 }
 
-// ---- many rows: one WARP per row.  With thousands of rows every SM holds dozens of independent warps, each with all of
-// its row's loads in flight at once, which a CTA walking its rows one after another (a chain of three barriers per
-// row) cannot match: LayerNorm -> int8 of 32768 x 2048 ran at 1.1 TB/s with a CTA per row.  Lane l holds the vectors
-// k * 32 + l (k < VEC), cols = VEC * 256.
 __device__ __forceinline__ float warp_reduce(float v, bool is_max)
 {
 #pragma unroll
@@ -127,57 +152,7 @@ __device__ __forceinline__ float warp_reduce(float v, bool is_max)
     return v;
 }
 
-template <int VEC>
-__device__ __forceinline__ void warp_quantize_row(const float (&x)[VEC * 8], int8_t* __restrict__ q_row, float* __restrict__ scale_out, int lane)
-{
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < VEC * 8; i++) amax = fmaxf(amax, fabsf(x[i]));
-    amax = warp_reduce(amax, true);
-    const float sc = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
-    if (lane == 0) *scale_out = sc;
-#pragma unroll
-    for (int k = 0; k < VEC; k++) {
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int t = 0; t < 4; t++) {
-            lo |= (uint32_t)(uint8_t)quant_one(x[k * 8 + t], sc) << (8 * t);
-            hi |= (uint32_t)(uint8_t)quant_one(x[k * 8 + 4 + t], sc) << (8 * t);
-        }
-        *reinterpret_cast<uint2*>(q_row + (size_t)(k * 32 + lane) * 8) = make_uint2(lo, hi);
-    }
-}
-
-template <int VEC>
-__device__ __forceinline__ void warp_layernorm_quantize_row(float (&x)[VEC * 8], const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                            float eps, int8_t* __restrict__ q_row, float* __restrict__ scale_out, int lane)
-{
-    constexpr int COLS = VEC * 256;
-    float s = 0.0f;
-#pragma unroll
-    for (int i = 0; i < VEC * 8; i++) s += x[i];
-    const float mean = warp_reduce(s, false) / (float)COLS;
-    float v2 = 0.0f;
-#pragma unroll
-    for (int i = 0; i < VEC * 8; i++) { const float d = x[i] - mean; v2 += d * d; }
-    const float inv = 1.0f / sqrtf(warp_reduce(v2, false) / (float)COLS + eps);
-#pragma unroll
-    for (int k = 0; k < VEC; k++) {
-        const int col = (k * 32 + lane) * 8;
-        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + col)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + col + 4));
-        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + col)), b1 = __ldg(reinterpret_cast<const float4*>(beta + col + 4));
-        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-        for (int t = 0; t < 8; t++) {
-            const float h = __fadd_rn(__fmul_rn(__fmul_rn(x[k * 8 + t] - mean, inv), g[t]), b[t]);
-            x[k * 8 + t] = ns_bf16_bits_to_f32(ns_f32_to_bf16_bits(h));
-        }
-    }
-    warp_quantize_row<VEC>(x, q_row, scale_out, lane);
-}
-
-// Rows at and above this count take the warp-per-row kernels.
+// Rows at and above this count take the many-row kernels of ns_rows_stream.cu.
 constexpr int64_t MANY_ROWS = 2048;
 
 // CTA shape for rows of `cols` elements (cols % 256 == 0): threads = min(256, cols / 8), vectors per thread = cols / 8 /
@@ -196,3 +171,9 @@ inline bool row_shape(int cols, unsigned* threads, int* vpt)
 }
 
 }  // namespace ns_rows
+
+// Many bf16 rows at once through rings of row buffers in shared memory (ns_rows_stream.cu).
+bool ns_rows_stream_fits(bool layernorm, int64_t rows, int cols);
+cudaError_t ns_rows_stream_quantize(NsDevice* d, const uint16_t* x, int64_t rows, int cols, int8_t* q, float* scale);
+cudaError_t ns_rows_stream_layernorm(NsDevice* d, const uint16_t* x, const float* gamma, const float* beta, int64_t rows, int cols, float eps, int8_t* q,
+                                     float* scale);

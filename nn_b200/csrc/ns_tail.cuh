@@ -160,14 +160,11 @@ __device__ __forceinline__ void quantize_row(const float (&x)[VPT * 8], bool on,
     const float sc = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
     if (threadIdx.x == 0) *scale_out = sc;
     if (!on) return;
+    const float rcp = __frcp_rn(sc);
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int t = 0; t < 4; t++) {
-            lo |= (uint32_t)(uint8_t)ns_rows::quant_one(x[j * 8 + t], sc) << (8 * t);
-            hi |= (uint32_t)(uint8_t)ns_rows::quant_one(x[j * 8 + 4 + t], sc) << (8 * t);
-        }
+        uint32_t lo, hi;
+        ns_rows::quant8<true>(x + j * 8, sc, rcp, lo, hi);
         *reinterpret_cast<uint2*>(q_row + vec_col(j, active)) = make_uint2(lo, hi);
     }
 }
@@ -302,7 +299,7 @@ __device__ __forceinline__ void gelu_rows(const NsTail& t, ns_rows::RowShared& s
                 float f[8];
                 dequant8(t, acc, a_scale, col, f);
 #pragma unroll
-                for (int i = 0; i < 8; i++) v[j * 8 + i] = ns_bf16_bits_to_f32(ns_f32_to_bf16_bits(ns_gelu_tanh(f[i])));
+                for (int i = 0; i < 8; i++) v[j * 8 + i] = ns_bf16_bits_to_f32(ns_f32_to_bf16_bits(ns_gelu_fast(f[i])));
             }
         }
         __syncthreads();   // x_scale[r] has been read by every thread before thread 0 overwrites it (q_scale may be the same array)

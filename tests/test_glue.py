@@ -10,12 +10,18 @@ from nn_b200 import native as N
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 16), (5, 100), (64, 2048), (33, 8192), (130, 512), (2500, 2048), (2100, 4096), (2049, 1024)])
+@pytest.mark.parametrize("rows,cols", [(1, 16), (5, 100), (64, 2048), (33, 8192), (130, 512), (2500, 2048), (2100, 4096), (2049, 1024),
+                                       (2060, 8192), (20000, 2048), (10000, 8192), (9000, 4096), (30000, 1024)])
 def test_quantize_rows_bit_exact(dev, orc, rows, cols):
+    """The many-row cases are sized so that every row group of the streaming kernels goes round its ring of buffers more than once."""
     x = orc.normal((rows, cols), 81, 1.5)
     x[0, :] = 0.0  # all-zero row -> scale 1
     if rows > 2:
         x[2, 0] = 1e-30
+    if rows > 3:
+        # scale exactly 1 and quotients on half-integers: ties go to even, through the kernels' exact-division path
+        x[3, :] = np.clip(x[3, :] * 20.0, -126.0, 126.0)
+        x[3, :16] = [127.0, 0.5, 1.5, 2.5, -0.5, -1.5, 126.5, -126.5, 63.5, 64.5, -3.5, 4.5, 0.25, 0.75, -0.75, 100.5]
     for dtype, host in ((N.NS_F32, x), (N.NS_BF16, orc.round_bf16(x))):
         dx = dev.from_numpy(host)
         dq, ds = dev.empty(rows * cols, N.NS_I8), dev.empty(rows)
@@ -26,7 +32,35 @@ def test_quantize_rows_bit_exact(dev, orc, rows, cols):
         assert np.array_equal(q, dq.download((rows, cols)))
 
 
-@pytest.mark.parametrize("rows,cols", [(3, 128), (64, 2048), (7, 8192), (40, 512), (2500, 2048), (2049, 1024), (2050, 4096)])
+@pytest.mark.parametrize("cols", [1024, 2048, 8192])
+def test_quantize_rows_odd_values_agree_between_kernels(dev, orc, cols):
+    """Rows with NaNs, infinities or only subnormal values: the many-row kernels find them by their maximum and round them with
+    the plain divisions, so they must give the bytes and scales the few-row kernel (a CTA per row) gives for the same rows."""
+    rows = 2100
+    x = orc.round_bf16(orc.normal((rows, cols), 83, 1.5)).copy()
+    x[5, 7] = 0x7FC0                                  # NaN
+    x[9, 100] = 0x7F80                                # +infinity
+    x[11, 3], x[11, 900] = 0xFF80, 0x7FC0             # -infinity and a NaN
+    x[20, :] = (np.arange(cols) % 0x7F + 1).astype(np.uint16)          # subnormals only: the scale has no float reciprocal
+    x[21, :] = 0x8001
+    x[30, :] = 0x7FC0                                 # nothing but NaNs
+    dx = dev.from_numpy(x)
+    dq, ds = dev.empty(rows * cols, N.NS_I8), dev.empty(rows)
+    N.call("ns_quantize_rows_i8", dev.handle, dx.ptr, N.NS_BF16, C.c_int64(rows), cols, dq.ptr, ds.ptr)
+    dq2, ds2 = dev.empty(rows * cols, N.NS_I8), dev.empty(rows)
+    for r0 in range(0, rows, 700):
+        N.call("ns_quantize_rows_i8", dev.handle, C.c_uint64(dx.ptr + r0 * cols * 2), N.NS_BF16, C.c_int64(700), cols, C.c_uint64(dq2.ptr + r0 * cols),
+               C.c_uint64(ds2.ptr + r0 * 4))
+    dev.synchronize()
+    assert np.array_equal(ds.download().view(np.uint32), ds2.download().view(np.uint32))
+    assert np.array_equal(dq.download((rows, cols)), dq2.download((rows, cols)))
+    # and the untouched rows follow the rule
+    q, sc = orc.quantize_rows_i8(x[100:200])
+    assert np.array_equal(q, dq.download((rows, cols))[100:200]) and np.array_equal(sc, ds.download()[100:200])
+
+
+@pytest.mark.parametrize("rows,cols", [(3, 128), (64, 2048), (7, 8192), (40, 512), (2500, 2048), (2049, 1024), (2050, 4096), (20000, 2048),
+                                       (30000, 1024)])
 def test_layernorm_variants(dev, orc, rows, cols):
     x = orc.normal((rows, cols), 91, 2.0)
     g, b = orc.normal((cols,), 92, 0.5, 1.0), orc.normal((cols,), 93, 0.1)
