@@ -365,6 +365,12 @@ NS_API int ns_linear_forward_partial(ns_device_t dev, ns_linear_t linear, uint64
  * layernorm_fused_f32 PtxKernels.Decoding.cs:61-90) for a row-split or K-split product.  q_scale may be x_scale. */
 NS_API int ns_finish_norm_quant(ns_device_t dev, uint64_t partial, int splits, ns_linear_t linear, uint64_t x_scale, uint64_t residual,
                                 int64_t rows, uint64_t x_out, uint64_t gamma, uint64_t beta, float eps, uint64_t q, uint64_t q_scale);
+/* q, q_scale = int8 row quantisation of bf16(GELU(((float) sum_s partial[s,m,n] * x_scale[m]) * w_scale[n] + bias[n])): the input
+ * of FF2 straight from FF1's partial sums.  Replaces Linear + BiasGelu (Layers/Attention.cs:207-209; bias_gelu_f32,
+ * PtxKernels.Decoding.cs:93-114) for a K-split product followed by the next product's row quantisation.  N_local a multiple of
+ * 256 up to 8192, buffers 16-byte aligned; q_scale may be x_scale. */
+NS_API int ns_finish_gelu_quant(ns_device_t dev, uint64_t partial, int splits, ns_linear_t linear, uint64_t x_scale, int64_t rows, uint64_t q,
+                                uint64_t q_scale);
 /* qkv[m, 0:3d] = bf16(dequantised partial sums + bias) of the fused QKV product, and its K and V thirds appended to the cache
  * at position pos_dev[0] + step (as ns_kv_append).  Replaces the product's epilogue + KeyValueWrite
  * (Layers/Attention.cs:98-118; kv_write_f32 PtxKernels.Decoding.cs:130-143). */

@@ -66,7 +66,6 @@ ns_gemv_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const int8
 {
     constexpr int GV_COLS = gv_cols(MR);
     __shared__ int red[2][GV_MAX_WARPS][GV_COLS][MR];
-    ns_pdl_wait();
     ns_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int col_begin = (int)((int64_t)blockIdx.x * p.N / gridDim.x);
@@ -85,8 +84,17 @@ ns_gemv_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const int8
         for (int c = 0; c < CPW; c++)
             wv[slot][c] = (n < col_end && kv[c]) ? gv_load_stream(w + (size_t)n * p.K + kb[c]) : make_int4(0, 0, 0, 0);
     };
+    // A Linear's weights are written by no kernel on the stream: their first columns are fetched while the kernel before this
+    // one is still running (the launch is programmatic); everything else waits for it.
+    if (p.prefetch_b) {
 #pragma unroll
-    for (int s = 0; s < GV_COLS; s++) load_col(s, col_begin + s);
+        for (int s = 0; s < GV_COLS; s++) load_col(s, col_begin + s);
+    }
+    ns_pdl_wait();
+    if (!p.prefetch_b) {
+#pragma unroll
+        for (int s = 0; s < GV_COLS; s++) load_col(s, col_begin + s);
+    }
 
     // this lane's activation bytes, all rows
     int4 x[CPW][MR];

@@ -177,6 +177,57 @@ __global__ void ns_finish_norm_quant_reg_kernel(const FinishNormParams p)
     }
 }
 
+// Sum of the splits + dequantisation + bias + GELU, rounded to bf16 (what the product's own epilogue would have stored), then
+// the int8 row quantisation of that: the input of FF2 straight from FF1's partial sums.  One CTA per row, the row in registers.
+struct FinishGeluParams {
+    const int32_t* partial;
+    int splits;
+    const float* x_scale;
+    const float* w_scale;
+    const float* bias;
+    int64_t rows;
+    int cols;
+    int8_t* q;
+    float* q_scale;
+};
+
+template <int VPT>
+__global__ void ns_finish_gelu_quant_kernel(const FinishGeluParams p)
+{
+    ns_pdl_wait();
+    ns_pdl_trigger();
+    __shared__ ns_rows::RowShared sh;
+    const size_t slab = (size_t)p.rows * p.cols;
+    int it = 0;
+    for (int64_t r = blockIdx.x; r < p.rows; r += gridDim.x, it ^= 1) {
+        const float a_scale = p.x_scale[r];
+        float v[VPT * 8];
+#pragma unroll
+        for (int j = 0; j < VPT; j++) {
+            const int col = ns_rows::vec_col(j);
+            const size_t idx = (size_t)r * p.cols + col;
+            int32_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int sp = 0; sp < p.splits; sp++) {
+                const int4* src = reinterpret_cast<const int4*>(p.partial + (size_t)sp * slab + idx);
+                const int4 a = src[0], b = src[1];
+                acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+                acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+            }
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.w_scale + col)), w1 = __ldg(reinterpret_cast<const float4*>(p.w_scale + col + 4));
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col)), b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col + 4));
+            const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float t = ns_gelu_fast(__fadd_rn(__fmul_rn(__fmul_rn(__int2float_rn(acc[i]), a_scale), ws[i]), bs[i]));
+                v[j * 8 + i] = ns_bf16_bits_to_f32(ns_f32_to_bf16_bits(t));
+            }
+        }
+        // (x_scale[r] has been read by every thread before the barrier of the reduction: q_scale may be the same array)
+        ns_rows::quantize_row<VPT>(v, p.q + (size_t)r * p.cols, p.q_scale + r, sh.red[it]);
+    }
+}
+
 cudaError_t launch_finish_reg(NsDevice* d, unsigned threads, int vpt, const FinishNormParams& p)
 {
     const int64_t cap = (int64_t)d->sm_count * 8;
@@ -299,6 +350,43 @@ extern "C" int ns_finish_norm_quant(ns_device_t h, uint64_t partial, int splits,
     }
     const int64_t cap = (int64_t)d->sm_count * 8;
     NS_CUDA(ns_launch_plain(ns_finish_norm_quant_kernel, dim3((unsigned)(rows < cap ? rows : cap)), dim3(FUSED_THREADS), smem, d->stream, p));
+    return NS_OK;
+}
+
+extern "C" int ns_finish_gelu_quant(ns_device_t h, uint64_t partial, int splits, ns_linear_t linear, uint64_t x_scale, int64_t rows, uint64_t q,
+                                    uint64_t q_scale)
+{
+    NsDevice* d = ns_dev(h);
+    int rc = ns_device_make_current(d);
+    if (rc != NS_OK) return rc;
+    int n_loc = 0, mode = 0;
+    uint64_t w_scale = 0, bias = 0;
+    rc = ns_linear_info(linear, nullptr, &n_loc, &mode, nullptr, &w_scale, &bias);
+    if (rc != NS_OK) return rc;
+    NS_REQUIRE(mode == NS_I8 && w_scale != 0 && bias != 0, NS_ERR_ARGUMENT, "ns_finish_gelu_quant: the layer must be an int8 layer with a bias");
+    NS_REQUIRE(partial && x_scale && q && q_scale && splits >= 1 && rows >= 0, NS_ERR_ARGUMENT, "ns_finish_gelu_quant: bad argument");
+    unsigned threads = 0;
+    int vpt = 0;
+    NS_REQUIRE(((partial | q | w_scale | bias) & 15) == 0 && ns_rows::row_shape(n_loc, &threads, &vpt), NS_ERR_ARGUMENT,
+               "ns_finish_gelu_quant: rows of %d columns (a multiple of 256 up to 8192, buffers 16-byte aligned) expected", n_loc);
+    if (rows == 0) return NS_OK;
+    FinishGeluParams p;
+    p.partial = reinterpret_cast<const int32_t*>(partial);
+    p.splits = splits;
+    p.x_scale = reinterpret_cast<const float*>(x_scale);
+    p.w_scale = reinterpret_cast<const float*>(w_scale);
+    p.bias = reinterpret_cast<const float*>(bias);
+    p.rows = rows;
+    p.cols = n_loc;
+    p.q = reinterpret_cast<int8_t*>(q);
+    p.q_scale = reinterpret_cast<float*>(q_scale);
+    const int64_t cap = (int64_t)d->sm_count * 8;
+    const dim3 grid((unsigned)(rows < cap ? rows : cap)), block(threads);
+    switch (vpt) {
+        case 1: NS_CUDA(ns_launch_plain(ns_finish_gelu_quant_kernel<1>, grid, block, 0, d->stream, p)); break;
+        case 2: NS_CUDA(ns_launch_plain(ns_finish_gelu_quant_kernel<2>, grid, block, 0, d->stream, p)); break;
+        default: NS_CUDA(ns_launch_plain(ns_finish_gelu_quant_kernel<4>, grid, block, 0, d->stream, p)); break;
+    }
     return NS_OK;
 }
 

@@ -169,6 +169,10 @@ class GptW8A8:
         # passes of up to this many rows take one kernel per operator instead (their products are one-launch streaming
         # kernels with the epilogue inside)
         self.unfused_rows = GEMV_MAX_ROWS
+        # True: FF1's split sum + bias + GELU + quantisation as ONE row kernel (ns_finish_gelu_quant) instead of the product's own
+        # second kernel + the row quantisation.  Measured on the 24-layer model, batch 64: 2.44-2.50 ms per step against 2.40-2.42
+        # (64 CTAs do the GELU of 8192 columns that 512 do otherwise), so it stays off.
+        self.ff1_finish = False
         # True: decode attention quantises its output rows itself (ns_attention_decode_quant: one launch less per layer).
         # Measured on the 24-layer model, batch 64: 2.49 ms per step against 2.44 with the row kernel of its own (the last
         # CTA of a row works alone while the others have left), so it stays off.
@@ -296,9 +300,12 @@ class GptW8A8:
             N.call("ns_finish_norm_quant", h, C.c_uint64(part), sp, L["out"].handle, self.hq_scale.ptr, x_in.ptr, C.c_int64(m), x_out.ptr,
                    L["ln2"][0].ptr, L["ln2"][1].ptr, eps, self.hq.ptr, self.hq_scale.ptr)
             x_in, x_out = x_out, x_in
-            # (FF1 keeps its own bias + GELU epilogue: moving the GELU of 8192 columns into a 64-CTA row kernel was slower)
-            L["ff1"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS_GELU, N.NS_BF16, self.ffh.ptr)
-            N.call("ns_quantize_rows_i8", h, self.ffh.ptr, N.NS_BF16, C.c_int64(m), self.ff_loc, self.hq.ptr, self.hq_scale.ptr)
+            if self.ff1_finish and self._row_shape_ok(self.ff_loc):
+                part, sp = L["ff1"].forward_partial(self.hq.ptr, m)
+                N.call("ns_finish_gelu_quant", h, C.c_uint64(part), sp, L["ff1"].handle, self.hq_scale.ptr, C.c_int64(m), self.hq.ptr, self.hq_scale.ptr)
+            else:
+                L["ff1"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS_GELU, N.NS_BF16, self.ffh.ptr)
+                N.call("ns_quantize_rows_i8", h, self.ffh.ptr, N.NS_BF16, C.c_int64(m), self.ff_loc, self.hq.ptr, self.hq_scale.ptr)
             part, sp = L["ff2"].forward_partial(self.hq.ptr, m)
             if i + 1 < len(self.layers):
                 g, bta = self.layers[i + 1]["ln1"]

@@ -82,6 +82,7 @@ SIGNATURES = {
     "ns_linear_forward_host": [vp, vp, vp, i32, i32, vp, i32],
     "ns_linear_forward_partial": [vp, vp, u64, i32, P(u64), P(i32)],
     "ns_finish_norm_quant": [vp, u64, i32, vp, u64, u64, i64, u64, u64, u64, f32, u64, u64],
+    "ns_finish_gelu_quant": [vp, u64, i32, vp, u64, i64, u64, u64],
     "ns_finish_kv_append": [vp, u64, i32, vp, u64, i32, i32, u64, vp, u64, i32, u64],
     "ns_linear_forward_norm_quant": [vp, vp, u64, u64, u64, i64, u64, u64, u64, f32, u64, u64],
     "ns_linear_forward_gelu_quant": [vp, vp, u64, u64, i64, u64, u64],

@@ -271,6 +271,13 @@ def test_one_launch_gelu_quant_equals_two_launches(dev, orc, M, K, NN, tune):
             dev.synchronize()
             assert np.array_equal(q.download(), q_ref.download()), f"repetition {rep}"
             assert np.array_equal(s.download().view(np.uint32), s_ref.download().view(np.uint32)), f"repetition {rep}"
+        # the two-launch form of the decoding step: partial sums, then one row kernel for sum + bias + GELU + quantisation
+        q2, s2 = dev.zeros(M * NN, N.NS_I8), dev.zeros(M)
+        part, sp = _partial(dev, lin, xq, M)
+        N.call("ns_finish_gelu_quant", dev.handle, C.c_uint64(part), sp, lin, xs.ptr, C.c_int64(M), q2.ptr, s2.ptr)
+        dev.synchronize()
+        assert np.array_equal(q2.download(), q_ref.download())
+        assert np.array_equal(s2.download().view(np.uint32), s_ref.download().view(np.uint32))
     finally:
         dev.tune(0, 0)
     N.call("ns_linear_destroy", lin)
