@@ -44,13 +44,27 @@ NS_DEVINL void rs_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint3
                  : "memory");
 }
 
+// One try with a suspend-time hint: the warp sleeps in the instruction until the phase completes or about `ns` nanoseconds have
+// passed, instead of spinning through issue slots that the group's working warps need.
+NS_DEVINL bool rs_try_wait(uint32_t bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 NS_DEVINL bool rs_wait(uint32_t bar, uint32_t parity)
 {
-    if (ns_mbar_try_wait(bar, parity)) return true;
+    if (rs_try_wait(bar, parity, 20000u)) return true;
     const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!ns_mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xFF) == 0 && clock64() - t0 > NS_WAIT_LIMIT_CYCLES) return false;
+    while (!rs_try_wait(bar, parity, 20000u)) {
+        if (clock64() - t0 > NS_WAIT_LIMIT_CYCLES) return false;
     }
     return true;
 }
