@@ -128,6 +128,16 @@ constexpr long long NS_WAIT_LIMIT_CYCLES = 2000000000LL;
 
 // Waits until the kernel this one depends on has completed and its writes are visible (no-op otherwise).
 NS_DEVINL void ns_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// griddepcontrol.wait orders memory for the hardware; for the compiler it is an asm statement that clobbers memory, and a load
+// the compiler knows to be from read-only memory (__ldg, a const __restrict__ pointer) may still be scheduled above it.  A
+// kernel that does work before its wait passes every pointer to data of the kernel before it through this, after the
+// wait: the pointer then comes out of an asm statement that follows the wait, and so do the loads through it.
+template <class T>
+NS_DEVINL const T* ns_after_wait(const T* ptr)
+{
+    asm volatile("" : "+l"(ptr) : : "memory");
+    return ptr;
+}
 // Lets the next kernel on the stream start its prologue.
 NS_DEVINL void ns_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -446,6 +446,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
         int local = 0;
         bool ok = true;
         ns_pdl_wait();   // a_scale, residual and every output buffer belong to the previous kernel until it is done
+        const float* a_scales = ns_after_wait(p.a_scale);
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, local++) {
             int tm, tn, split;
             tile_coords(p, item, tm, tn, split);
@@ -459,7 +460,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
             // biases into L1 (each tile has other columns, so without this every 32-column chunk below would wait
             // for a round trip to L2).
             // (a product that only leaves exact accumulators, p.out == null, has no scales or bias)
-            cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok && p.k_splits == 1 && p.out != nullptr) ? __ldg(&p.a_scale[cx.row]) : 1.0f;
+            cx.a_scale = (KIND == NS_KIND_I8 && cx.row_ok && p.k_splits == 1 && p.out != nullptr) ? __ldg(&a_scales[cx.row]) : 1.0f;
             if (p.k_splits == 1 && warp == 2 && p.out != nullptr) {
                 const int pc = tn * BN + (lane & 7) * 32;
                 if (lane < BN / 32 && pc < p.N) {

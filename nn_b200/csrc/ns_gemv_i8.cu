@@ -66,7 +66,6 @@ ns_gemv_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const int8
 {
     constexpr int GV_COLS = gv_cols(MR);
     __shared__ int red[2][GV_MAX_WARPS][GV_COLS][MR];
-    ns_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int col_begin = (int)((int64_t)blockIdx.x * p.N / gridDim.x);
     const int col_end = (int)((int64_t)(blockIdx.x + 1) * p.N / gridDim.x);
@@ -91,6 +90,9 @@ ns_gemv_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const int8
         for (int s = 0; s < GV_COLS; s++) load_col(s, col_begin + s);
     }
     ns_pdl_wait();
+    ns_pdl_trigger();       // after the wait, as everywhere in the library: with the trigger before it, replayed graphs of a step gave other tokens
+    a = ns_after_wait(a);                                   // the activations and their scales are the previous kernel's
+    const float* a_scales = ns_after_wait(p.a_scale);
     if (!p.prefetch_b) {
 #pragma unroll
         for (int s = 0; s < GV_COLS; s++) load_col(s, col_begin + s);
@@ -107,7 +109,7 @@ ns_gemv_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const int8
     // the threads of the epilogue: thread t finishes (row t / GV_COLS, column t % GV_COLS) of every group
     const int f_row = threadIdx.x / GV_COLS, f_col = threadIdx.x % GV_COLS;
     const bool f_row_ok = threadIdx.x < GV_COLS * MR && f_row < p.M;
-    const float a_scale = (f_row_ok && p.out != nullptr) ? __ldg(&p.a_scale[f_row]) : 1.0f;
+    const float a_scale = (f_row_ok && p.out != nullptr) ? __ldg(&a_scales[f_row]) : 1.0f;
     constexpr int LANES_PER_ROW = 32 / MR;
 
     int buf = 0;

@@ -89,6 +89,8 @@ ns_stream_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const in
     }
     ns_pdl_wait();
     ns_pdl_trigger();
+    a = ns_after_wait(a);                                   // the activations and their scales are the previous kernel's
+    const float* a_scales = ns_after_wait(p.a_scale);
     if (!p.prefetch_b) {
 #pragma unroll
         for (int s = 0; s < G; s++) load_tile(s, tile_begin + s);
@@ -111,7 +113,7 @@ ns_stream_i8_kernel(const NsGemmParams p, const int8_t* __restrict__ a, const in
     const int f_mt = f_pair / G, f_s = f_pair % G;
     const int f_row = f_mt * 16 + (f_lane >> 2) + 8 * f_hi;
     const bool f_active = f_pair < MT * G && f_row < p.M;
-    const float a_scale = (f_active && p.out != nullptr) ? __ldg(&p.a_scale[f_row]) : 1.0f;
+    const float a_scale = (f_active && p.out != nullptr) ? __ldg(&a_scales[f_row]) : 1.0f;
 
     for (int t0 = tile_begin; t0 < tile_end; t0 += G) {
         // operands of this round's epilogue, in flight while the round is summed
