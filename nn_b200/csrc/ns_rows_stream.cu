@@ -106,7 +106,6 @@ __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16
     float* xchg = reinterpret_cast<float*>(rs_smem + Cfg::XCHG_OFFSET) + group * Cfg::XCHG_WORDS;
     const bool producer = sub == 0 && lane == 0;
 
-    ns_pdl_trigger();
     if (producer) {
 #pragma unroll
         for (int s = 0; s < STAGES; s++) ns_mbar_init(bar0 + 8 * s, 1);
@@ -114,6 +113,7 @@ __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16
     }
     __syncthreads();
     ns_pdl_wait();      // x (and gamma, beta) may be the work of the kernel before this one
+    ns_pdl_trigger();
 
     const int64_t n_groups = (int64_t)gridDim.x * Cfg::GROUPS;
     const int64_t first = (int64_t)blockIdx.x * Cfg::GROUPS + group;
