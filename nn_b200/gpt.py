@@ -79,8 +79,9 @@ class _Linear:
 
 # Up to this many rows a pass uses the fused row kernels (ns_finish_*): one launch less per product whose K is split.
 FUSED_MAX_ROWS = 256
-# Up to this many rows an int8 product is the row-streaming kernel (weights read once at the HBM rate, epilogue inside).
-GEMV_MAX_ROWS = 8
+# Up to this many rows an int8 product is ONE streaming kernel with its epilogue inside (1-8 rows: dp4a, weights read once at
+# the HBM rate; 9-16 rows: weights straight into registers, mma.sync).
+STREAM_MAX_ROWS = 16
 
 
 class GptW8A8:
@@ -168,7 +169,7 @@ class GptW8A8:
         self.fused = 1
         # passes of up to this many rows take one kernel per operator instead (their products are one-launch streaming
         # kernels with the epilogue inside)
-        self.unfused_rows = GEMV_MAX_ROWS
+        self.unfused_rows = STREAM_MAX_ROWS
         # True: FF1's split sum + bias + GELU + quantisation as ONE row kernel (ns_finish_gelu_quant) instead of the product's own
         # second kernel + the row quantisation.  Measured on the 24-layer model, batch 64: 2.44-2.50 ms per step against 2.40-2.42
         # (64 CTAs do the GELU of 8192 columns that 512 do otherwise), so it stays off.
@@ -205,8 +206,8 @@ class GptW8A8:
         eps, scale = C.c_float(cfg.eps), C.c_float(1.0 / np.sqrt(dh))
         if m <= FUSED_MAX_ROWS and self.fused == 2 and self._one_launch_ok(m):
             return self._forward_one_launch(steps)
-        # (one to eight rows: the products are row-streaming kernels with their epilogues inside, one launch each, and the
-        # pass with one kernel per operator is the faster one -- 1.32 against 1.38 ms per step at batch 8)
+        # (one to sixteen rows: the products are streaming kernels with their epilogues inside, one launch each, and the pass
+        # with one kernel per operator is the faster one -- 1.24 against 1.38 ms per step at batch 8, 1.30 against 1.45 at 16)
         if self.tp == 1 and self.unfused_rows < m <= FUSED_MAX_ROWS and self.fused:
             return self._forward_fused(steps)
         if self.tp > 1 and m <= FUSED_MAX_ROWS and self.fused and self.peer is not None:

@@ -7,8 +7,12 @@ bar in its own test (int32 accumulators bit-exact, bf16 outputs 1e-2).  End to e
 float epilogues run in the oracle's order; what differs (softmax and LayerNorm summation order, exp2 / tanh
 approximations) is far below a bf16 ulp and is absorbed by the rounding to bf16 and then to int8 that follows every
 operator -- unless a value sits on a rounding boundary, which moves one quantisation step of one product input.  On the
-configurations below no such flip occurs: the logits come out bit-identical (largest error printed by the test: 0).
-The bar is therefore the benchmark configuration's bf16 tolerance, 1e-2 * max(1, |e|); then a free-running generation through the
+first two configurations below no such flip occurs: the logits come out bit-identical (largest error printed by the
+test: 0) and the bar is the benchmark configuration's bf16 tolerance, 1e-2 * max(1, |e|).  The third (12 sequences: the
+decoding steps take the one-launch streaming products for 9 to 16 rows) does have one -- the GELU of the product epilogues
+is evaluated through ex2 / rcp approximations, 1e-6 relative from the oracle's tanhf form, and 12 x 8 x 512 x 2 hidden
+values give a bf16 rounding boundary a chance -- and one bf16 step of a residual-stream value near 1 (2^-7) moves a
+logit by about 1e-2: that configuration is held to 2e-2.  Then a free-running generation through the
 CUDA graph, which must reproduce the teacher-forced run's tokens exactly (GraphReplay, DecodingTests.cs:144-189) and
 hit the context reset of CharGpt.cs:276-283.
 """
@@ -28,17 +32,17 @@ TOL = 1e-2
 WORST = {"err": 0.0}
 
 
-def _check_step(orc, exp_logits, got_logits, step):
+def _check_step(orc, exp_logits, got_logits, step, tol=TOL):
     WORST["err"] = max(WORST["err"], float(orc.max_err(exp_logits, got_logits)))
-    assert orc.close(exp_logits, got_logits, TOL), f"step {step}: logits differ by {orc.max_err(exp_logits, got_logits):.3e}"
+    assert orc.close(exp_logits, got_logits, tol), f"step {step}: logits differ by {orc.max_err(exp_logits, got_logits):.3e}"
     top2 = np.sort(exp_logits, axis=1)[:, -2:]
-    clear = (top2[:, 1] - top2[:, 0]) > 2 * TOL * np.maximum(1.0, np.abs(top2[:, 1]))
+    clear = (top2[:, 1] - top2[:, 0]) > 2 * tol * np.maximum(1.0, np.abs(top2[:, 1]))
     agree = orc.argmax(exp_logits) == orc.argmax(got_logits)
     assert np.all(agree | ~clear), f"step {step}: argmax differs on rows {np.where(~agree & clear)[0]}"
     return int((~clear).sum())
 
 
-@pytest.mark.parametrize("batch,prompt_len,n_new,context", [(3, 20, 10, 64), (2, 10, 30, 32)])
+@pytest.mark.parametrize("batch,prompt_len,n_new,context", [(3, 20, 10, 64), (2, 10, 30, 32), (12, 8, 6, 32)])
 def test_teacher_forced_and_graph(dev, orc, batch, prompt_len, n_new, context):
     cfg = GptConfig(vocab=320, dim=256, heads=2, layers=2, ff_dim=512, context=context)
     w = om.make_weights(cfg, seed=4)
@@ -47,12 +51,13 @@ def test_teacher_forced_and_graph(dev, orc, batch, prompt_len, n_new, context):
     exp_tokens, exp_resets = ref.generate(prompt, n_new)
 
     model = GptW8A8(dev, cfg, w, batch, max_prefill=max(prompt_len, context // 2))
+    tol = TOL if batch < 9 else 2 * TOL
     # ---- teacher-forced, no graph: the device consumes the oracle's tokens
     history = [list(r) for r in prompt]
     near_ties, step = 0, 0
     model.prefill(np.array([h[-min(len(h), context - 1):] for h in history], dtype=np.int32))
     dev.synchronize()
-    near_ties += _check_step(orc, ref.logit_trace[0], model.read_logits(), 0)
+    near_ties += _check_step(orc, ref.logit_trace[0], model.read_logits(), 0, tol)
     for s in range(1, n_new):
         for b in range(batch):
             history[b].append(int(exp_tokens[b, s - 1]))
@@ -63,7 +68,7 @@ def test_teacher_forced_and_graph(dev, orc, batch, prompt_len, n_new, context):
             N.call("ns_h2d", dev.handle, C.c_uint64(model.ids.ptr), forced.ctypes.data_as(C.c_void_p), C.c_uint64(forced.nbytes))
             model.step(use_graph=False)
         dev.synchronize()
-        near_ties += _check_step(orc, ref.logit_trace[s], model.read_logits(), s)
+        near_ties += _check_step(orc, ref.logit_trace[s], model.read_logits(), s, tol)
     # ---- free-running through the graph
     tokens, resets = model.generate(prompt, n_new, use_graph=True)
     assert resets == exp_resets
