@@ -112,3 +112,33 @@ def test_recorded_step_survives_a_growing_scratch_block(orc):
     assert np.array_equal(out[0], out[1])
     fresh.synchronize()
     fresh.close()
+
+
+def test_many_row_prompt_read(dev, orc):
+    """More than 256 rows: the pass with one kernel per operator and flash attention over whole sequences (the shape of the
+    benchmark's prompt read).  The flash-attention kernel rounds the softmax weights to bf16 before the P V product and is held
+    to the oracle's attention at 1e-2 in its own test; over three layers the logits are held to 5e-2 here (measured: 2.2e-2).
+    The pass is reproducible bit for bit, cache included, and the tokens generated after it are the same through the graph
+    and through direct launches."""
+    cfg = GptConfig(vocab=320, dim=256, heads=2, layers=3, ff_dim=512, context=160)
+    w = om.make_weights(cfg, seed=6)
+    batch, prompt_len = 4, 100
+    prompt = orc.token_ids((batch, prompt_len), 46, cfg.vocab).astype(np.int32)
+    ref = om.W8A8Decoder(cfg, w, batch)
+    ref.generate(prompt.astype(np.int64), 1)
+    out = []
+    for use_graph in (True, False):
+        model = GptW8A8(dev, cfg, w, batch, max_prefill=prompt_len)
+        model.prefill(prompt)
+        dev.synchronize()
+        logits, cache = model.read_logits().copy(), model.kv_block.download().copy()
+        tokens, _ = model.generate(prompt, 6, use_graph=use_graph)
+        out.append((logits, cache, tokens))
+        model.close()
+    err = orc.max_err(ref.logit_trace[0], out[0][0])
+    print(f"many-row prompt read: largest logit error {err:.3e}")
+    assert orc.close(ref.logit_trace[0], out[0][0], 5e-2), err
+    assert out[0][1].any()
+    assert np.array_equal(out[0][0].view(np.uint32), out[1][0].view(np.uint32))
+    assert np.array_equal(out[0][1], out[1][1])
+    assert np.array_equal(out[0][2], out[1][2])
