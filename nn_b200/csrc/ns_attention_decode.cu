@@ -28,7 +28,16 @@ struct NsKvCache {
 namespace {
 
 constexpr int DEC_THREADS = 128;
-constexpr int DEC_CHUNK = 1024;  // positions per CTA (scores kept in shared memory)
+// The cache of a row is walked in CHUNKS of `chunk` positions, [chunk k, chunk (k + 1)), whatever the batch, the grid or the
+// split of the work: every chunk yields its own (maximum, sum, weighted values) triple, computed from the chunk alone, and a
+// row's result is the fold of its chunks' triples in chunk order with one fixed formula (fold_chunk).  One CTA that owns the
+// whole row folds in registers; several CTAs per row write their chunks' triples to scratch memory and
+// ns_attention_combine_kernel folds them -- the same operations in the same order, so a row's output bits do not depend on how
+// many sequences share the GPU (a sequence decoded in a batch equals the sequence decoded alone: DecodingTests.cs:100-142
+// holds the reference to that).  The chunk length is a function of the cache's capacity alone (decode_chunk): two chunks up
+// to 2048 positions, about 1024 positions each beyond (a chunk costs a block-wide reduction of the weighted values; with
+// 256-position chunks a 64-sequence step lost 8 % to them).
+constexpr int DEC_MAX_CHUNK = 1024;      // scores of a chunk are kept in shared memory
 
 struct DecodeParams {
     const uint16_t* q;  // element (b, i, h, d) at q[(b * steps + i) * q_stride + h * dh + d]
@@ -41,8 +50,11 @@ struct DecodeParams {
     int max_pages, page_size, page_shift, heads;
     const int32_t* pos_dev;
     int batch, steps, splits;
+    int chunk;              // positions per chunk (a multiple of 64, at most DEC_MAX_CHUNK)
+    int max_chunks;         // chunks of the longest possible context: triple slots per row in `partial`
+    int chunks_per_split;   // consecutive chunks one CTA owns
     float scale;
-    float* partial;  // [rows, splits, 2 + dh] when splits > 1
+    float* partial;  // [rows, max_chunks, 2 + dh] when splits > 1
     // optional: int8 row quantisation of the output (the next product's input) by the last CTA to finish a row
     int8_t* q_out;          // [batch * steps, heads * dh] or null
     float* q_scale;         // [batch * steps]
@@ -70,6 +82,18 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8])
         f[2 * t] = __uint_as_float(w[t] << 16);
         f[2 * t + 1] = __uint_as_float(w[t] & 0xFFFF0000u);
     }
+}
+
+// (M, L, O) <- (M, L, O) folded with the triple (m, l, o) of the next chunk; every product and sum rounded on its own so that
+// the kernels that fold give the same bits.  The first chunk of a row is taken as it is.
+__device__ __forceinline__ void fold_chunk(bool first, float& M, float& L, float& O, float m, float l, float o)
+{
+    if (first) { M = m; L = l; O = o; return; }
+    const float M2 = fmaxf(M, m);
+    const float a = expf(M - M2), b = expf(m - M2);
+    L = __fadd_rn(__fmul_rn(L, a), __fmul_rn(l, b));
+    O = __fadd_rn(__fmul_rn(O, a), __fmul_rn(o, b));
+    M = M2;
 }
 
 // The output row (b, i) -- all heads of one token -- is complete when `heads` CTAs have stored their 128 (or 64, 32)
@@ -135,7 +159,7 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
     constexpr int GROUPS = DEC_THREADS / LPR;  // rows in flight per CTA
     // U = load rounds in flight per lane (a round = one cached row per lane group): two when thousands of CTAs share the
     // SMs, four when the grid is small and a CTA's own chain of loads is what its time consists of
-    __shared__ float s_scores[DEC_CHUNK];
+    __shared__ float s_scores[DEC_MAX_CHUNK];
     __shared__ float s_red[DEC_THREADS / 32];
     __shared__ float s_acc[GROUPS][DH];
 
@@ -147,21 +171,17 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
     const int h = idx % p.heads;
     const int b = idx / p.heads;
     const int kv_len = p.pos_dev[0] + i + 1;
-    const int per_split = (((kv_len + p.splits - 1) / p.splits + p.page_size - 1) >> p.page_shift) << p.page_shift;
-    const int j0 = split * per_split;
-    const int j1 = min(kv_len, j0 + per_split);
+    const int n_chunks = (kv_len + p.chunk - 1) / p.chunk;
+    const int k0 = split * p.chunks_per_split;
+    const int k1 = min(n_chunks, k0 + p.chunks_per_split);
     const int row_id = (b * p.heads + h) * p.steps + i;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = threadIdx.x % LPR;       // which pieces of a row this lane owns
     const int grp = threadIdx.x / LPR;       // row slot of this lane inside the CTA
     const int page_mask = p.page_size - 1;
 
-    float m_run = -INFINITY, l_run = 0.0f;
-    float acc[4][8];
-#pragma unroll
-    for (int c = 0; c < 4; c++)
-#pragma unroll
-        for (int d = 0; d < 8; d++) acc[c][d] = 0.0f;
+    // running fold of this CTA's chunks (one CTA per row): thread d < DH holds column d of the weighted values
+    float M_run = 0.0f, L_run = 0.0f, O_run = 0.0f;
 
     float qf[4][8];
     {
@@ -177,8 +197,14 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
         return pool + (size_t)page * p.heads * slab + head_off + (size_t)(j & page_mask) * DH;
     };
 
-    for (int c0 = j0; c0 < j1; c0 += DEC_CHUNK) {
-        const int c1 = min(j1, c0 + DEC_CHUNK);
+    for (int k = k0; k < k1; k++) {
+        const int c0 = k * p.chunk;
+        const int c1 = min(kv_len, c0 + p.chunk);
+        float acc[4][8];
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+            for (int d = 0; d < 8; d++) acc[c][d] = 0.0f;
         // ---- scores: s_j = (q . k_j) * scale; U rounds of four loads per lane are in flight before any is used.
         // Loop bounds are uniform per warp because the reduction shuffles need every lane.
         for (int jb = c0 + warp * RPW; jb < c1; jb += (DEC_THREADS / 32) * RPW * U) {
@@ -212,19 +238,17 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
             }
         }
         __syncthreads();
-        // ---- chunk maximum, rescale of the running state, exponentials
+        // ---- the chunk's own maximum and exponentials
         float mx = -INFINITY;
         for (int j = threadIdx.x; j < c1 - c0; j += DEC_THREADS) mx = fmaxf(mx, s_scores[j]);
         mx = warp_max_f(mx);
         if (lane == 0) s_red[warp] = mx;
         __syncthreads();
         mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-        const float m_new = fmaxf(m_run, mx);
-        const float alpha = m_run == -INFINITY ? 0.0f : expf(m_run - m_new);
         __syncthreads();
         float sum = 0.0f;
         for (int j = threadIdx.x; j < c1 - c0; j += DEC_THREADS) {
-            const float e = expf(s_scores[j] - m_new);
+            const float e = expf(s_scores[j] - mx);
             s_scores[j] = e;
             sum += e;
         }
@@ -232,13 +256,7 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
         if (lane == 0) s_red[warp] = sum;
         __syncthreads();
         sum = s_red[0] + s_red[1] + s_red[2] + s_red[3];
-        l_run = l_run * alpha + sum;
-        m_run = m_new;
-#pragma unroll
-        for (int c = 0; c < 4; c++)
-#pragma unroll
-            for (int d = 0; d < 8; d++) acc[c][d] *= alpha;
-        // ---- o += p_j * v_j ; row slot `grp` walks rows grp, grp + GROUPS, ...
+        // ---- o_g = sum of p_j * v_j over the rows of slot `grp`: rows grp, grp + GROUPS, ... of the chunk
         for (int jb = c0 + grp; jb < c1; jb += GROUPS * U) {
             uint4 vv[U][4];
             float pj[U];
@@ -266,25 +284,29 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
                     for (int d = 0; d < 8; d++) acc[c][d] = fmaf(pj[u], vf[d], acc[c][d]);
                 }
         }
+        // ---- the chunk's weighted values: the GROUPS slots summed in slot order
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+            for (int d = 0; d < 8; d++) s_acc[grp][(sub + LPR * c) * 8 + d] = acc[c][d];
+        __syncthreads();
+        for (int d = threadIdx.x; d < DH; d += DEC_THREADS) {
+            float t = 0.0f;
+#pragma unroll 8
+            for (int gg = 0; gg < GROUPS; gg++) t += s_acc[gg][d];
+            if (p.splits == 1) {
+                fold_chunk(k == k0, M_run, L_run, O_run, mx, sum, t);
+            } else {
+                float* dst = p.partial + ((size_t)row_id * p.max_chunks + k) * (2 + DH);
+                dst[2 + d] = t;
+                if (d == 0) { dst[0] = mx; dst[1] = sum; }
+            }
+        }
         __syncthreads();
     }
-    // ---- reduce the GROUPS partial outputs
-#pragma unroll
-    for (int c = 0; c < 4; c++)
-#pragma unroll
-        for (int d = 0; d < 8; d++) s_acc[grp][(sub + LPR * c) * 8 + d] = acc[c][d];
-    __syncthreads();
-    for (int d = threadIdx.x; d < DH; d += DEC_THREADS) {
-        float t = 0.0f;
-#pragma unroll 8
-        for (int gg = 0; gg < GROUPS; gg++) t += s_acc[gg][d];
-        if (p.splits == 1) {
-            p.o[(size_t)(b * p.steps + i) * p.o_stride + h * DH + d] = ns_f32_to_bf16_bits(t / l_run);
-        } else {
-            float* dst = p.partial + ((size_t)row_id * p.splits + split) * (2 + DH);
-            dst[2 + d] = t;
-            if (d == 0) { dst[0] = m_run; dst[1] = l_run; }
-        }
+    if (p.splits == 1) {
+        for (int d = threadIdx.x; d < DH; d += DEC_THREADS)
+            p.o[(size_t)(b * p.steps + i) * p.o_stride + h * DH + d] = ns_f32_to_bf16_bits(O_run / L_run);
     }
     if (p.q_out != nullptr && p.splits == 1) {
         __shared__ int last_cta;
@@ -302,21 +324,15 @@ __global__ void ns_attention_combine_kernel(const DecodeParams p)
     const int i = row_id % p.steps;
     const int h = (row_id / p.steps) % p.heads;
     const int b = row_id / (p.steps * p.heads);
-    const float* src = p.partial + (size_t)row_id * p.splits * (2 + DH);
-    float m = -INFINITY;
-    for (int s = 0; s < p.splits; s++) m = fmaxf(m, src[s * (2 + DH)]);
-    float l = 0.0f;
-    for (int s = 0; s < p.splits; s++) {
-        const float ms = src[s * (2 + DH)];
-        if (ms != -INFINITY) l += src[s * (2 + DH) + 1] * expf(ms - m);
-    }
+    const int n_chunks = (p.pos_dev[0] + i + 1 + p.chunk - 1) / p.chunk;
+    const float* src = p.partial + (size_t)row_id * p.max_chunks * (2 + DH);
     for (int d = threadIdx.x; d < DH; d += blockDim.x) {
-        float t = 0.0f;
-        for (int s = 0; s < p.splits; s++) {
-            const float ms = src[s * (2 + DH)];
-            if (ms != -INFINITY) t += src[s * (2 + DH) + 2 + d] * expf(ms - m);
+        float M = 0.0f, L = 0.0f, O = 0.0f;
+        for (int k = 0; k < n_chunks; k++) {
+            const float* t = src + (size_t)k * (2 + DH);
+            fold_chunk(k == 0, M, L, O, t[0], t[1], t[2 + d]);
         }
-        p.o[(size_t)(b * p.steps + i) * p.o_stride + h * DH + d] = ns_f32_to_bf16_bits(t / l);
+        p.o[(size_t)(b * p.steps + i) * p.o_stride + h * DH + d] = ns_f32_to_bf16_bits(O / L);
     }
     if (p.q_out != nullptr) {
         __shared__ int last_cta;
@@ -590,21 +606,23 @@ int ns_kv_cache_view(ns_kv_cache_t ch, NsKvCacheView* out)
 }
 
 // Scratch bytes ns_attention_decode needs for `rows` = batch * heads * steps query rows split `splits` ways.
-static size_t decode_scratch_bytes(int rows, int splits, int dh) { return (size_t)rows * splits * (2 + dh) * sizeof(float); }
+static size_t decode_scratch_bytes(int rows, int max_chunks, int dh) { return (size_t)rows * max_chunks * (2 + dh) * sizeof(float); }
 
-static int choose_splits(const NsDevice* d, int rows, int max_len, int page_size)
+// Positions per chunk for a cache of `max_len` positions: a function of the capacity alone, so that every launch on that
+// cache -- whatever its batch -- cuts a row the same way.
+static int decode_chunk(int max_len)
 {
-    int splits = 1;
-    const int target = 2 * d->sm_count;
-    if (rows < target) {
-        splits = (target + rows - 1) / rows;
-        int by_len = max_len / 256;
-        if (by_len < 1) by_len = 1;
-        if (splits > by_len) splits = by_len;
-        if (splits > 32) splits = 32;
-    }
-    (void)page_size;
-    return splits < 1 ? 1 : splits;
+    int n = (max_len + DEC_MAX_CHUNK - 1) / DEC_MAX_CHUNK;
+    if (n < 2) n = 2;
+    int c = ((max_len + n - 1) / n + 63) / 64 * 64;
+    return c > DEC_MAX_CHUNK ? DEC_MAX_CHUNK : c;
+}
+
+// CTAs per row: one per chunk when the rows alone do not fill the SMs twice, else one.
+static int choose_splits(const NsDevice* d, int rows, int max_chunks)
+{
+    if (rows >= 2 * d->sm_count) return 1;
+    return max_chunks > 32 ? 32 : max_chunks;
 }
 
 int ns_attention_decode_impl(NsDevice* d, NsKvCache* c, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride, uint64_t page_table,
@@ -634,10 +652,14 @@ int ns_attention_decode_impl(NsDevice* d, NsKvCache* c, uint64_t q, int64_t q_st
     }
     const int rows = batch * c->heads * steps;
     // the context length lives on the device; the split count is sized for the longest possible context
-    p.splits = choose_splits(d, rows, max_pages * c->page_size, c->page_size);
+    p.chunk = decode_chunk(max_pages * c->page_size);
+    p.max_chunks = (max_pages * c->page_size + p.chunk - 1) / p.chunk;
+    p.splits = choose_splits(d, rows, p.max_chunks);
+    p.chunks_per_split = (p.max_chunks + p.splits - 1) / p.splits;
+    p.splits = (p.max_chunks + p.chunks_per_split - 1) / p.chunks_per_split;      // no CTA without a chunk
     p.partial = nullptr;
     if (p.splits > 1) {
-        const size_t need = decode_scratch_bytes(rows, p.splits, c->head_dim);
+        const size_t need = decode_scratch_bytes(rows, p.max_chunks, c->head_dim);
         if (own_scratch) {
             void* s = nullptr;
             int rc = ns_scratch_reserve(d, need, &s);

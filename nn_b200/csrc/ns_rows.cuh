@@ -127,7 +127,7 @@ __device__ __forceinline__ void layernorm_quantize_row(float (&x)[VPT * 8], cons
     const float mean = block_reduce(s, false, sh.red[0]) / (float)cols;
     float v2 = 0.0f;
 #pragma unroll
-    for (int i = 0; i < VPT * 8; i++) { const float d = x[i] - mean; v2 += d * d; }
+    for (int i = 0; i < VPT * 8; i++) { const float d = x[i] - mean; v2 = fmaf(d, d, v2); }
     const float inv = 1.0f / sqrtf(block_reduce(v2, false, sh.red[1]) / (float)cols + eps);
 #pragma unroll
     for (int j = 0; j < VPT; j++) {

@@ -32,7 +32,8 @@ struct RsCfg {
     static constexpr int PARAM_BYTES = LN ? COLS * 8 : 0;         // gamma and beta as float
     static constexpr int BAR_OFFSET = RING_BYTES + PARAM_BYTES;
     static constexpr int XCHG_OFFSET = BAR_OFFSET + GROUPS * STAGES * 8;
-    static constexpr int XCHG_WORDS = 2 * 5 * WPR;                // per group: two row parities x (four reductions + the verdict) x warps
+    static constexpr int NV = COLS / 256;                         // 32-vector pieces of a row: a sum is taken piece by piece, in piece order
+    static constexpr int XCHG_WORDS = 2 * 5 * NV;                 // per group: two row parities x (four reductions + the verdict) x pieces (>= warps)
     static constexpr int SMEM_BYTES = XCHG_OFFSET + GROUPS * XCHG_WORDS * 4;
     static_assert(COLS % (WPR * 256) == 0 && VEC >= 1, "a lane holds whole 16-byte vectors");
 };
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16
     for (int64_t r = first; r < rows; r += n_groups, i++) {
         const int slot = i % STAGES;
         const bool ok = __all_sync(0xffffffffu, rs_wait(bar0 + 8 * slot, (uint32_t)(i / STAGES) & 1u));   // one verdict per warp
-        float* words = xchg + (i & 1) * 5 * WPR;
+        float* words = xchg + (i & 1) * 5 * Cfg::NV;
         // reduction `which` (0..3) of this row over the group; with `first_of_row` the warps' verdicts travel along
         auto group_reduce = [&](float v, bool is_max, int which, bool first_of_row, bool* all_ok) {
             v = ns_rows::warp_reduce(v, is_max);
@@ -152,20 +153,53 @@ __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16
                 return v;
             }
             if (lane == 0) {
-                words[which * WPR + sub] = v;
-                if (first_of_row) words[4 * WPR + sub] = ok ? 1.0f : 0.0f;
+                words[which * Cfg::NV + sub] = v;
+                if (first_of_row) words[4 * Cfg::NV + sub] = ok ? 1.0f : 0.0f;
             }
             rs_group_barrier(group, WPR * 32);
-            float t = words[which * WPR];
+            float t = words[which * Cfg::NV];
 #pragma unroll
-            for (int w = 1; w < WPR; w++) t = is_max ? fmaxf(t, words[which * WPR + w]) : t + words[which * WPR + w];
+            for (int w = 1; w < WPR; w++) t = is_max ? fmaxf(t, words[which * Cfg::NV + w]) : t + words[which * Cfg::NV + w];
             if (first_of_row) {
                 bool a = true;
 #pragma unroll
-                for (int w = 0; w < WPR; w++) a = a && words[4 * WPR + w] != 0.0f;
+                for (int w = 0; w < WPR; w++) a = a && words[4 * Cfg::NV + w] != 0.0f;
                 *all_ok = a;
             }
             return t;
+        };
+        // A SUM over the row in the order of the few-row kernels (ns_rows::block_reduce with one vector per thread): vector by
+        // vector (its eight elements left to right, done by the caller), the 32 vectors of a piece by the xor-shuffle tree, the
+        // pieces one after the other -- so LayerNorm gives the same bits whichever kernel family a pass takes (rows of up to
+        // 2048 columns, where the few-row kernels hold one vector per thread).  part[k] is this lane's vector of piece
+        // sub * VEC + k.
+        auto group_sum = [&](const float (&part)[VEC], int which, bool first_of_row, bool* all_ok) {
+            float t[VEC];
+#pragma unroll
+            for (int k = 0; k < VEC; k++) t[k] = ns_rows::warp_reduce(part[k], false);
+            if (WPR == 1) {
+                if (first_of_row) *all_ok = ok;
+                float r = t[0];
+#pragma unroll
+                for (int k = 1; k < VEC; k++) r += t[k];
+                return r;
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int k = 0; k < VEC; k++) words[which * Cfg::NV + sub * VEC + k] = t[k];
+                if (first_of_row) words[4 * Cfg::NV + sub] = ok ? 1.0f : 0.0f;
+            }
+            rs_group_barrier(group, WPR * 32);
+            float r = words[which * Cfg::NV];
+#pragma unroll
+            for (int v = 1; v < Cfg::NV; v++) r += words[which * Cfg::NV + v];
+            if (first_of_row) {
+                bool a = true;
+#pragma unroll
+                for (int w = 0; w < WPR; w++) a = a && words[4 * Cfg::NV + w] != 0.0f;
+                *all_ok = a;
+            }
+            return r;
         };
         uint4 raw[VEC];
         if (ok) {
@@ -239,17 +273,25 @@ __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[k * 8 + j] = t[j];
             }
-            float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float part[VEC];
 #pragma unroll
-            for (int j = 0; j < VEC * 8; j++) s4[j & 3] += v[j];
-            const float mean = group_reduce((s4[0] + s4[1]) + (s4[2] + s4[3]), false, 0, true, &all_ok) / (float)COLS;
+            for (int k = 0; k < VEC; k++) {
+                float t = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) t += v[k * 8 + j];
+                part[k] = t;
+            }
+            const float mean = group_sum(part, 0, true, &all_ok) / (float)COLS;
             if (!all_ok) { failed = true; break; }
             if (producer && next < rows) issue(slot, next);
 #pragma unroll
-            for (int j = 0; j < 4; j++) s4[j] = 0.0f;
+            for (int k = 0; k < VEC; k++) {
+                float t = 0.0f;
 #pragma unroll
-            for (int j = 0; j < VEC * 8; j++) { v[j] -= mean; s4[j & 3] = fmaf(v[j], v[j], s4[j & 3]); }
-            const float inv = 1.0f / sqrtf(group_reduce((s4[0] + s4[1]) + (s4[2] + s4[3]), false, 1, false, nullptr) / (float)COLS + eps);
+                for (int j = 0; j < 8; j++) { v[k * 8 + j] -= mean; t = fmaf(v[k * 8 + j], v[k * 8 + j], t); }
+                part[k] = t;
+            }
+            const float inv = 1.0f / sqrtf(group_sum(part, 1, false, nullptr) / (float)COLS + eps);
             uint32_t m[2] = {0u, 0u};
 #pragma unroll
             for (int k = 0; k < VEC; k++) {

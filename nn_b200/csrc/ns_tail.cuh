@@ -193,7 +193,7 @@ __device__ __forceinline__ void layernorm_quantize_row(float (&x)[VPT * 8], bool
     float v2 = 0.0f;
     if (on) {
 #pragma unroll
-        for (int i = 0; i < VPT * 8; i++) { const float d = x[i] - mean; v2 += d * d; }
+        for (int i = 0; i < VPT * 8; i++) { const float d = x[i] - mean; v2 = fmaf(d, d, v2); }
     }
     const float inv = 1.0f / sqrtf(block_reduce(v2, false, sh.red[1]) / (float)cols + eps);
     if (on) {

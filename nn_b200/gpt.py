@@ -79,6 +79,10 @@ class _Linear:
 
 # Up to this many rows a pass uses the fused row kernels (ns_finish_*): one launch less per product whose K is split.
 FUSED_MAX_ROWS = 256
+# A prompt of at least this many positions read from position 0 (head_dim 128) takes the flash-attention kernel, a shorter one
+# the cached-attention kernel -- by the prompt's length alone, whatever the batch, so that a sequence read in a batch and the
+# same sequence read alone go through the same arithmetic.
+FLASH_MIN_STEPS = 128
 # Up to this many rows an int8 product is ONE streaming kernel with its epilogue inside (1-8 rows: dp4a, weights read once at
 # the HBM rate; 9-16 rows: weights straight into registers, mma.sync).
 STREAM_MAX_ROWS = 16
@@ -216,7 +220,7 @@ class GptW8A8:
         N.call("ns_embed_pos", h, self.ids.ptr, self.tok.ptr, self.pos_table.ptr, N.NS_BF16, self.pos.ptr, B, steps, D, cfg.vocab, cfg.context,
                N.NS_BF16, x_in.ptr)
         self._n += 1
-        whole_sequence = steps > 1 and self.length == 0 and dh == 128
+        whole_sequence = self._whole_sequence(steps)
         for li, (L, cache) in enumerate(zip(self.layers, self.caches)):
             N.call("ns_layernorm", h, x_in.ptr, N.NS_BF16, L["ln1"][0].ptr, L["ln1"][1].ptr, C.c_int64(m), D, eps, N.NS_I8, self.hq.ptr, self.hq_scale.ptr)
             L["qkv"].forward(self.hq.ptr, self.hq_scale.ptr, m, N.EPI_BIAS, N.NS_BF16, self.qkv.ptr)
@@ -264,10 +268,21 @@ class GptW8A8:
         self._n += 1
         self.x = [x_in, x_out]
 
+    def _whole_sequence(self, steps: int) -> bool:
+        return steps >= FLASH_MIN_STEPS and self.length == 0 and self.cfg.head_dim == 128
+
     def _attention_rows(self, cache, B: int, steps: int, scale) -> None:
         """Cached attention of the new positions, output rows quantised for the output projection (hq, hq_scale)."""
         h, dl, m = self.dev.handle, self.d_loc, B * steps
-        if self.attn_quant and m <= 4000:
+        if self._whole_sequence(steps):
+            dh = self.cfg.head_dim
+            q, k, v = self.qkv.ptr, self.qkv.ptr + 2 * dl, self.qkv.ptr + 4 * dl
+            st_in = (C.c_int64 * 3)(steps * 3 * dl, dh, 3 * dl)
+            st_out = (C.c_int64 * 3)(steps * dl, dh, dl)
+            N.call("ns_attention_prefill", h, C.c_uint64(q), C.c_uint64(k), C.c_uint64(v), self.attn.ptr, B, self.heads_loc, steps, dh,
+                   st_in, st_in, st_in, st_out, scale, 1)
+            N.call("ns_quantize_rows_i8", h, self.attn.ptr, N.NS_BF16, C.c_int64(m), dl, self.hq.ptr, self.hq_scale.ptr)
+        elif self.attn_quant and m <= 4000:
             N.call("ns_attention_decode_quant", h, cache, C.c_uint64(self.qkv.ptr), C.c_int64(3 * dl), self.attn.ptr, C.c_int64(dl), self.page_table.ptr,
                    self.max_pages, self.pos.ptr, B, steps, scale, self.hq.ptr, self.hq_scale.ptr)
             self._n -= 1

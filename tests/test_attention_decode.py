@@ -167,3 +167,33 @@ def test_append_outside_the_cache_is_skipped_and_reported(dev, orc):
     N.call("ns_kv_append", dev.handle, cache, k.ptr, v.ptr, C.c_int64(heads * dh), table.ptr, max_pages, pos.ptr, B, 1)
     dev.synchronize()
     N.call("ns_kv_cache_destroy", cache)
+
+
+@pytest.mark.parametrize("cap,length", [(768, 1), (768, 383), (768, 384), (768, 385), (768, 700), (2048, 1500), (4096, 3000), (128, 100)])
+def test_a_sequence_in_a_batch_equals_the_sequence_in_a_small_batch(dev, orc, cap, length):
+    """The reference's BatchedDecoding property (DecodingTests.cs:100-142), bit for bit: with 64 sequences every (sequence,
+    head) row is one CTA's; with 4 sequences the cache of a row is split over several CTAs and merged by a second kernel.  The
+    kernels walk a row's cache in the same chunks (384 positions for a cache of 768, 1024 for 2048 or 4096) and fold the chunks'
+    partial results in the same order with the same operations, so the output bits must not depend on the batch the sequence
+    is decoded in."""
+    heads, dh, page_size = 8, 128, 16
+    scale = 1.0 / np.sqrt(dh)
+    B = 64
+    k = orc.round_bf16(orc.normal((B, length, heads, dh), 21))
+    v = orc.round_bf16(orc.normal((B, length, heads, dh), 22))
+    q = orc.round_bf16(orc.normal((B, 1, heads, dh), 23, 2.0))
+
+    def run(rows):
+        cache = Cache(dev, len(rows), heads, dh, cap, page_size, shuffle_seed=9)
+        cache.append(k[rows].reshape(len(rows), length, -1), v[rows].reshape(len(rows), length, -1), length)
+        cache.advance(length - 1)
+        out = cache.attend(q[rows].reshape(len(rows), 1, -1), 1, scale)
+        cache.close()
+        return out
+
+    big = run(list(range(B)))
+    for rows in ([0, 1, 2, 3], [60, 61, 62, 63], [17]):
+        small = run(rows)
+        assert np.array_equal(small, big[rows]), f"sequences {rows} differ between a batch of {len(rows)} and a batch of {B}"
+    exp = orc.attention_slice(orc.widen_bf16(q[5, :, 3]), orc.widen_bf16(k[5, :, 3]), orc.widen_bf16(v[5, :, 3]), length - 1, scale)
+    assert orc.close(orc.bf16_round_trip(exp), orc.widen_bf16(big[5, :, 3]), TOL)

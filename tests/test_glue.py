@@ -59,6 +59,26 @@ def test_quantize_rows_odd_values_agree_between_kernels(dev, orc, cols):
     assert np.array_equal(q, dq.download((rows, cols))[100:200]) and np.array_equal(sc, ds.download()[100:200])
 
 
+@pytest.mark.parametrize("cols", [1024, 2048])
+def test_layernorm_int8_is_the_same_in_both_kernel_families(dev, orc, cols):
+    """2100 rows at once take the many-row kernel, the same rows 700 at a time the few-row kernel (a CTA per row).  Both sum a
+    row vector by vector, 32 vectors by the same shuffle tree, piece after piece, so that a sequence read in a large batch and
+    the same sequence read alone get the same bits (rows of up to 2048 columns: one vector per thread in the few-row kernel)."""
+    rows = 2100
+    x = orc.round_bf16(orc.normal((rows, cols), 95, 2.0))
+    g, b = orc.normal((cols,), 96, 0.5, 1.0), orc.normal((cols,), 97, 0.1)
+    dx, dg, db = dev.from_numpy(x), dev.from_numpy(g), dev.from_numpy(b)
+    q1, s1 = dev.empty(rows * cols, N.NS_I8), dev.empty(rows)
+    N.call("ns_layernorm", dev.handle, dx.ptr, N.NS_BF16, dg.ptr, db.ptr, C.c_int64(rows), cols, C.c_float(1e-5), N.NS_I8, q1.ptr, s1.ptr)
+    q2, s2 = dev.empty(rows * cols, N.NS_I8), dev.empty(rows)
+    for r0 in range(0, rows, 700):
+        N.call("ns_layernorm", dev.handle, C.c_uint64(dx.ptr + r0 * cols * 2), N.NS_BF16, dg.ptr, db.ptr, C.c_int64(700), cols, C.c_float(1e-5), N.NS_I8,
+               C.c_uint64(q2.ptr + r0 * cols), C.c_uint64(s2.ptr + r0 * 4))
+    dev.synchronize()
+    assert np.array_equal(s1.download().view(np.uint32), s2.download().view(np.uint32))
+    assert np.array_equal(q1.download((rows, cols)), q2.download((rows, cols)))
+
+
 @pytest.mark.parametrize("rows,cols", [(3, 128), (64, 2048), (7, 8192), (40, 512), (2500, 2048), (2049, 1024), (2050, 4096), (20000, 2048),
                                        (30000, 1024)])
 def test_layernorm_variants(dev, orc, rows, cols):

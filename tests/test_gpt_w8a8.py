@@ -120,9 +120,9 @@ def test_many_row_prompt_read(dev, orc):
     to the oracle's attention at 1e-2 in its own test; over three layers the logits are held to 5e-2 here (measured: 2.2e-2).
     The pass is reproducible bit for bit, cache included, and the tokens generated after it are the same through the graph
     and through direct launches."""
-    cfg = GptConfig(vocab=320, dim=256, heads=2, layers=3, ff_dim=512, context=160)
+    cfg = GptConfig(vocab=320, dim=256, heads=2, layers=3, ff_dim=512, context=192)
     w = om.make_weights(cfg, seed=6)
-    batch, prompt_len = 4, 100
+    batch, prompt_len = 4, 130
     prompt = orc.token_ids((batch, prompt_len), 46, cfg.vocab).astype(np.int32)
     ref = om.W8A8Decoder(cfg, w, batch)
     ref.generate(prompt.astype(np.int64), 1)
@@ -142,3 +142,32 @@ def test_many_row_prompt_read(dev, orc):
     assert np.array_equal(out[0][0].view(np.uint32), out[1][0].view(np.uint32))
     assert np.array_equal(out[0][1], out[1][1])
     assert np.array_equal(out[0][2], out[1][2])
+
+
+@pytest.mark.parametrize("prompt_len,context", [(12, 64), (40, 64), (140, 192)])
+def test_a_sequence_in_a_batch_equals_the_sequence_alone(dev, orc, prompt_len, context):
+    """BatchedDecoding (DecodingTests.cs:100-142), bit for bit on the int8 decoder: 20 sequences together, three of them
+    together, and single ones must produce the same greedy tokens and the same logits.  The passes differ -- 20 sequences take
+    the many-row pass for the prompt and tcgen05 products with fused row kernels for the steps, few sequences the streaming
+    products with one kernel per operator, their attention splits the cache over several CTAs -- but every operator is exact
+    (integer sums), or sums in one fixed order (LayerNorm, the chunks of cached attention), or is chosen by the prompt's length
+    alone (flash attention from 128 positions on)."""
+    cfg = GptConfig(vocab=320, dim=256, heads=2, layers=2, ff_dim=512, context=context)
+    w = om.make_weights(cfg, seed=8)
+    B, n_new = 20, 10
+    prompt = orc.token_ids((B, prompt_len), 47, cfg.vocab).astype(np.int32)
+
+    def run(rows):
+        model = GptW8A8(dev, cfg, w, len(rows), max_prefill=prompt_len)
+        model.prefill(prompt[rows])
+        dev.synchronize()
+        logits = model.read_logits().copy()
+        tokens, _ = model.generate(prompt[rows], n_new, use_graph=True)
+        model.close()
+        return logits, tokens
+
+    big_logits, big_tokens = run(list(range(B)))
+    for rows in ([0, 1, 2], [19], [7], [4, 5, 6, 7, 8, 9, 10, 11, 12]):
+        logits, tokens = run(rows)
+        assert np.array_equal(logits.view(np.uint32), big_logits[rows].view(np.uint32)), f"prompt logits of sequences {rows} depend on the batch"
+        assert np.array_equal(tokens, big_tokens[rows]), f"tokens of sequences {rows} depend on the batch"
