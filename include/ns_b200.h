@@ -300,7 +300,10 @@ NS_API int ns_kv_append(ns_device_t dev, ns_kv_cache_t cache, uint64_t k, uint64
 
 /* o[b, i, h, :] = softmax_j((q[b, i, h, :] . K[b, j, h, :]) * scale) . V[b, j, h, :] over cached positions j <= pos + i.
  * q element (b, i, h, d) at q[(b * steps + i) * q_stride + h * head_dim + d], o likewise with o_stride.
- * Uses the device object's scratch block when the work is split along the cache. */
+ * Uses the device object's scratch block when the work is split along the cache.  The output bits of a row depend on the row's
+ * cached data, max_pages and the page size only, not on batch or steps (a sequence decoded in a batch equals the sequence
+ * decoded alone, as DecodingTests.cs:100-142 asks of the reference): the cache is walked in chunks fixed by its capacity and
+ * the chunks' partial results are folded in chunk order, by one CTA or by several. */
 NS_API int ns_attention_decode(ns_device_t dev, ns_kv_cache_t cache, uint64_t q, int64_t q_stride, uint64_t o, int64_t o_stride,
                                uint64_t page_table, int max_pages, uint64_t pos_dev, int batch, int steps, float scale);
 
