@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
     // U = load rounds in flight per lane (a round = one cached row per lane group): two when thousands of CTAs share the
     // SMs, four when the grid is small and a CTA's own chain of loads is what its time consists of
     __shared__ float s_scores[DEC_MAX_CHUNK];
-    __shared__ float s_red[DEC_THREADS / 32];
+    __shared__ float s_red[DEC_THREADS / 32], s_red2[DEC_THREADS / 32];
     __shared__ float s_acc[GROUPS][DH];
 
     ns_pdl_wait();
@@ -245,7 +245,6 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
         if (lane == 0) s_red[warp] = mx;
         __syncthreads();
         mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-        __syncthreads();
         float sum = 0.0f;
         for (int j = threadIdx.x; j < c1 - c0; j += DEC_THREADS) {
             const float e = expf(s_scores[j] - mx);
@@ -253,9 +252,9 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
             sum += e;
         }
         sum = warp_sum_f(sum);
-        if (lane == 0) s_red[warp] = sum;
+        if (lane == 0) s_red2[warp] = sum;      // (its own words: the maxima may still be being read)
         __syncthreads();
-        sum = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+        sum = s_red2[0] + s_red2[1] + s_red2[2] + s_red2[3];
         // ---- o_g = sum of p_j * v_j over the rows of slot `grp`: rows grp, grp + GROUPS, ... of the chunk
         for (int jb = c0 + grp; jb < c1; jb += GROUPS * U) {
             uint4 vv[U][4];
@@ -302,7 +301,8 @@ __global__ void __launch_bounds__(DEC_THREADS) ns_attention_decode_kernel(const 
                 if (d == 0) { dst[0] = mx; dst[1] = sum; }
             }
         }
-        __syncthreads();
+        // (no barrier here: the next chunk writes s_scores and s_red only after this one's last reads of them, which precede
+        // the barrier above, and s_acc only after three more barriers)
     }
     if (p.splits == 1) {
         for (int d = threadIdx.x; d < DH; d += DEC_THREADS)
