@@ -33,7 +33,7 @@ struct RsCfg {
     static constexpr int BAR_OFFSET = RING_BYTES + PARAM_BYTES;
     static constexpr int XCHG_OFFSET = BAR_OFFSET + GROUPS * STAGES * 8;
     static constexpr int NV = COLS / 256;                         // 32-vector pieces of a row: a sum is taken piece by piece, in piece order
-    static constexpr int XCHG_WORDS = 2 * 5 * NV;                 // per group: two row parities x (four reductions + the verdict) x pieces (>= warps)
+    static constexpr int XCHG_WORDS = 2 * 5 * NV;                 // per group: two row parities x (four reductions + the outcome of the wait) x pieces (>= warps)
     static constexpr int SMEM_BYTES = XCHG_OFFSET + GROUPS * XCHG_WORDS * 4;
     static_assert(COLS % (WPR * 256) == 0 && VEC >= 1, "a lane holds whole 16-byte vectors");
 };
@@ -143,9 +143,9 @@ __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16
     int i = 0;
     for (int64_t r = first; r < rows; r += n_groups, i++) {
         const int slot = i % STAGES;
-        const bool ok = __all_sync(0xffffffffu, rs_wait(bar0 + 8 * slot, (uint32_t)(i / STAGES) & 1u));   // one verdict per warp
+        const bool ok = __all_sync(0xffffffffu, rs_wait(bar0 + 8 * slot, (uint32_t)(i / STAGES) & 1u));   // one outcome per warp
         float* words = xchg + (i & 1) * 5 * Cfg::NV;
-        // reduction `which` (0..3) of this row over the group; with `first_of_row` the warps' verdicts travel along
+        // reduction `which` (0..3) of this row over the group; with `first_of_row` the outcomes of the warps' waits travel along
         auto group_reduce = [&](float v, bool is_max, int which, bool first_of_row, bool* all_ok) {
             v = ns_rows::warp_reduce(v, is_max);
             if (WPR == 1) {

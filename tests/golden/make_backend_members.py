@@ -13,7 +13,9 @@ import sys
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_backend_members.py <checkout of the reference>")
+    root = sys.argv[1]
     text = open(os.path.join(root, "src", "NeuralSharp", "Backends", "Backend.cs")).read()
     body = text[text.index("internal abstract class Backend"):text.index("internal static class CounterRandom")]
     members = {}
