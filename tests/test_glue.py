@@ -130,3 +130,26 @@ def test_embed_argmax_counter(dev, orc):
     N.call("ns_argmax_i32", dev.handle, dx.ptr, 5, 32000, C.c_int64(32000), di.ptr)
     dev.synchronize()
     assert np.array_equal(orc.argmax(x).astype(np.int32), di.download())
+
+
+def test_a_second_stream_waits_for_an_event_of_the_first(dev):
+    """Two device objects on one GPU are two streams.  The first fills 256 MB several times over and records an event; the
+    second waits for the event (ns_stream_wait_event) and copies the buffer: the copy must hold the last fill, every time."""
+    from nn_b200.device import Device
+    side = Device(dev.ordinal)
+    try:
+        n = 64 * 1024 * 1024
+        a, b = dev.empty(n), dev.empty(n)
+        ev = dev.event()
+        for rep in range(3):
+            for seed in range(4):      # keep the first stream busy, the last fill is the one that counts
+                N.call("ns_fill_normal", dev.handle, a.ptr, N.NS_F32, C.c_int64(n), 100 + 10 * rep + seed, C.c_float(0.0), C.c_float(1.0))
+            dev.record(ev)
+            side.wait_event(ev)
+            N.call("ns_d2d_async", side.handle, C.c_uint64(b.ptr), C.c_uint64(a.ptr), C.c_uint64(4 * n))
+            side.synchronize()
+            dev.synchronize()
+            got, want = b.download(count=4096, offset=n - 4096), a.download(count=4096, offset=n - 4096)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"repetition {rep}"
+    finally:
+        side.close()
