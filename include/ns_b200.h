@@ -82,13 +82,17 @@ NS_API int ns_device_status(ns_device_t dev, int* status);
  * kernel, NS_TUNE_NARROW = the narrowest tile, NS_TUNE_PAIR = the CTA-pair kernel wherever a shape allows it.
  * k_splits: 0 = heuristic, otherwise the split-K count; with NS_TUNE_PAIR, 2 = the pair kernel with its tiles' k-blocks dealt
  * out to the clusters in equal shares (the form large products take when their last wave of tiles would leave many clusters
- * idle), on any shape of at least four tiles.  A host binding has no reason to import this. */
+ * idle), on any shape of at least four tiles.  tile_n = NS_TUNE_DROP_ROW: the many-row kernels (ns_quantize_rows_i8 and
+ * ns_layernorm from 2048 rows on) leave out the copy of row k_splits, so that the bounded wait of that row's warps runs out
+ * (status 600 + warps per row) without anything faulting; any other call of ns_device_tune ends it.  A host binding has no
+ * reason to import this. */
 /* TEST HOOK, not for hosts: while `buffer` (device memory, 4 x 8 bytes per SM) is non-zero, every CTA of a product with a
  * second phase (ns_linear_forward_norm_quant and its siblings) records four times in nanoseconds there: kernel start,
  * product done, all CTAs arrived, rows done.  0 turns it off. */
 NS_API int ns_debug_tail_times(ns_device_t dev, uint64_t buffer);
 #define NS_TUNE_NARROW 32
 #define NS_TUNE_PAIR 512
+#define NS_TUNE_DROP_ROW 600
 NS_API int ns_device_tune(ns_device_t dev, int tile_n, int k_splits);
 
 /* ------------------------------------------------------------------------------------------------

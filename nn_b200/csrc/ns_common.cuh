@@ -63,6 +63,7 @@ struct NsDevice {
     // tuning overrides (0 = heuristic)
     int force_bn = 0;
     int force_splits = 0;
+    int rows_drop = -1;     // test hook: the many-row kernels leave out the copy of this row (its group's wait then runs out)
     int capturing = 0;
     // streams, events and staging buffers of the host-to-host pipeline (ns_linear_forward_host); made on first use
     void* host_pipe = nullptr;

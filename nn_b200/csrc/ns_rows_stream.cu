@@ -92,7 +92,7 @@ NS_DEVINL float rs_absmax_or_inf(uint32_t mm)
 template <int COLS, int WPR, int STAGES, bool LN>
 __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16_t* __restrict__ x, const float* __restrict__ gamma,
                                                                     const float* __restrict__ beta, int64_t rows, float eps, int8_t* __restrict__ q,
-                                                                    float* __restrict__ scale, int* status)
+                                                                    float* __restrict__ scale, int* status, int64_t drop_row)
 {
     using Cfg = RsCfg<COLS, WPR, STAGES, LN>;
     constexpr int VEC = Cfg::VEC;
@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16
     const int64_t n_groups = (int64_t)gridDim.x * Cfg::GROUPS;
     const int64_t first = (int64_t)blockIdx.x * Cfg::GROUPS + group;
     auto issue = [&](int slot, int64_t r) {
+        if (r == drop_row) return;      // test hook (-1 otherwise): this row's copy never comes
         ns_mbar_expect_tx(bar0 + 8 * slot, Cfg::ROW_BYTES);
         rs_bulk_load(ns_smem_u32(ring + (size_t)slot * Cfg::ROW_BYTES), x + (size_t)r * COLS, Cfg::ROW_BYTES, bar0 + 8 * slot);
     };
@@ -370,7 +371,7 @@ cudaError_t rs_launch(NsDevice* d, const uint16_t* x, const float* gamma, const 
     const int64_t cap = (int64_t)d->sm_count * per_sm;
     if (ctas > cap) ctas = cap;
     return ns_launch_plain(kernel, dim3((unsigned)ctas), dim3(RS_THREADS), (size_t)Cfg::SMEM_BYTES, d->stream, x, gamma, beta, rows, eps, q, scale,
-                           d->status_dev);
+                           d->status_dev, (int64_t)d->rows_drop);
 }
 
 }  // namespace

@@ -188,9 +188,15 @@ extern "C" int ns_device_tune(ns_device_t h, int tile_n, int k_splits)
 {
     NsDevice* d = ns_dev(h);
     NS_REQUIRE(d != nullptr, NS_ERR_ARGUMENT, "ns_device_tune: device is null");
-    NS_REQUIRE(tile_n == 0 || tile_n == NS_TUNE_NARROW || tile_n == 64 || tile_n == 128 || tile_n == 256 || tile_n == NS_TUNE_PAIR, NS_ERR_ARGUMENT,
-               "ns_device_tune: tile_n must be 0, 64, 128, 256, NS_TUNE_NARROW or NS_TUNE_PAIR");
+    NS_REQUIRE(tile_n == 0 || tile_n == NS_TUNE_NARROW || tile_n == 64 || tile_n == 128 || tile_n == 256 || tile_n == NS_TUNE_PAIR ||
+                   tile_n == NS_TUNE_DROP_ROW, NS_ERR_ARGUMENT,
+               "ns_device_tune: tile_n must be 0, 64, 128, 256, NS_TUNE_NARROW, NS_TUNE_PAIR or NS_TUNE_DROP_ROW");
     NS_REQUIRE(k_splits >= 0 && k_splits <= 64, NS_ERR_ARGUMENT, "ns_device_tune: k_splits must be in [0, 64]");
+    d->rows_drop = -1;
+    if (tile_n == NS_TUNE_DROP_ROW) {
+        d->rows_drop = k_splits;
+        return NS_OK;
+    }
     d->force_bn = tile_n;
     d->force_splits = k_splits;
     return NS_OK;

@@ -153,3 +153,32 @@ def test_a_second_stream_waits_for_an_event_of_the_first(dev):
             assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"repetition {rep}"
     finally:
         side.close()
+
+
+def test_many_row_kernel_gives_up_when_a_copy_never_arrives(dev, orc):
+    """Failure detection without a GPU fault: the test hook makes the many-row quantisation leave out the copy of one row.  The
+    warp that owns the row waits for it, gives up after about a second, reports status 600 + warps per row through the next
+    synchronisation (NS_ERR_KERNEL), waits once more for what it still has in flight and returns; the other rows are
+    finished, and the device stays usable."""
+    rows, cols = 4096, 2048
+    x = orc.round_bf16(orc.normal((rows, cols), 99, 1.5))
+    dx = dev.from_numpy(x)
+    dq, ds = dev.zeros(rows * cols, N.NS_I8), dev.zeros(rows)
+    dev.tune(600, 5)          # NS_TUNE_DROP_ROW: the copy of row 5 is left out
+    try:
+        N.call("ns_quantize_rows_i8", dev.handle, dx.ptr, N.NS_BF16, C.c_int64(rows), cols, dq.ptr, ds.ptr)
+        with pytest.raises(N.NsError) as err:
+            dev.synchronize()
+        assert "status 601" in str(err.value)
+    finally:
+        dev.tune(0, 0)
+    q, sc = orc.quantize_rows_i8(x)
+    got = dq.download((rows, cols))
+    assert not got[5].any(), "the row whose copy never came must not be written"
+    done = np.abs(got).max(axis=1) > 0                     # (no row of this input quantises to all zeros)
+    assert done.sum() >= rows - 8 and not done[5], "only rows of the group that gave up may be missing"
+    assert np.array_equal(got[done], q[done])
+    # the device is still usable
+    N.call("ns_quantize_rows_i8", dev.handle, dx.ptr, N.NS_BF16, C.c_int64(rows), cols, dq.ptr, ds.ptr)
+    dev.synchronize()
+    assert np.array_equal(dq.download((rows, cols)), q) and np.array_equal(ds.download(), sc)
