@@ -283,7 +283,8 @@ def test_one_launch_gelu_quant_equals_two_launches(dev, orc, M, K, NN, tune):
     N.call("ns_linear_destroy", lin)
 
 
-@pytest.mark.parametrize("B,steps,heads,dh,pos0", [(64, 1, 16, 128, 37), (3, 2, 4, 32, 0), (5, 1, 2, 64, 63), (64, 1, 2, 128, 600)])
+@pytest.mark.parametrize("B,steps,heads,dh,pos0", [(64, 1, 16, 128, 37), (3, 2, 4, 32, 0), (5, 1, 2, 64, 63), (64, 1, 2, 128, 600), (12, 1, 2, 128, 40),
+                                                  (4, 3, 2, 64, 5), (16, 1, 4, 128, 0), (1, 1, 2, 128, 9), (8, 1, 16, 128, 100)])
 def test_one_launch_kv_append_equals_unfused(dev, orc, B, steps, heads, dh, pos0):
     D = heads * dh
     K, NN, M = 256, 3 * heads * dh, B * steps
