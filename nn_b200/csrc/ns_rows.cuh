@@ -15,8 +15,10 @@ namespace ns_rows {
 
 constexpr int MAX_WARPS = 8;
 
+constexpr int MAX_VPT = 4;
+
 struct RowShared {
-    float red[3][MAX_WARPS];   // one set of per-warp partials per reduction of a row pass
+    float red[3][MAX_VPT * MAX_WARPS];   // one set of partials (a word per 32-vector piece of the row) per reduction of a row pass
 };
 
 __device__ __forceinline__ float block_reduce(float v, bool is_max, float* red)
@@ -32,6 +34,33 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* red)
     __syncthreads();
     float r = red[0];
     for (int w = 1; w < warps; w++) r = is_max ? fmaxf(r, red[w]) : r + red[w];
+    return r;
+}
+
+// A SUM over the row in the library's one order, whichever kernel takes it: vector by vector (part[j]: the eight elements of
+// this thread's vector j, left to right), the 32 vectors of a piece (a warp's vectors j) by the xor-shuffle tree, the pieces
+// one after the other in the order of their columns (piece j * warps + warp).  The many-row kernels (ns_rows_stream.cu) and the
+// second phase of the product kernel (ns_tail.cuh) sum in the same order, so LayerNorm gives the same bits in all of them.
+template <int VPT>
+__device__ __forceinline__ float block_sum_pieces(const float (&part)[VPT], float* red)
+{
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5;
+    float t[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        float v = part[j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        t[j] = v;
+    }
+    if (VPT == 1 && warps == 1) return t[0];
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+        for (int j = 0; j < VPT; j++) red[j * warps + warp] = t[j];
+    }
+    __syncthreads();
+    float r = red[0];
+    for (int w = 1; w < VPT * warps; w++) r += red[w];
     return r;
 }
 
@@ -121,14 +150,23 @@ __device__ __forceinline__ void layernorm_quantize_row(float (&x)[VPT * 8], cons
         g[j][0] = __ldg(reinterpret_cast<const float4*>(gamma + col)); g[j][1] = __ldg(reinterpret_cast<const float4*>(gamma + col + 4));
         b[j][0] = __ldg(reinterpret_cast<const float4*>(beta + col)); b[j][1] = __ldg(reinterpret_cast<const float4*>(beta + col + 4));
     }
-    float s = 0.0f;
+    float part[VPT];
 #pragma unroll
-    for (int i = 0; i < VPT * 8; i++) s += x[i];
-    const float mean = block_reduce(s, false, sh.red[0]) / (float)cols;
-    float v2 = 0.0f;
+    for (int j = 0; j < VPT; j++) {
+        float s = 0.0f;
 #pragma unroll
-    for (int i = 0; i < VPT * 8; i++) { const float d = x[i] - mean; v2 = fmaf(d, d, v2); }
-    const float inv = 1.0f / sqrtf(block_reduce(v2, false, sh.red[1]) / (float)cols + eps);
+        for (int i = 0; i < 8; i++) s += x[j * 8 + i];
+        part[j] = s;
+    }
+    const float mean = block_sum_pieces<VPT>(part, sh.red[0]) / (float)cols;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        float v2 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) { const float d = x[j * 8 + i] - mean; v2 = fmaf(d, d, v2); }
+        part[j] = v2;
+    }
+    const float inv = 1.0f / sqrtf(block_sum_pieces<VPT>(part, sh.red[1]) / (float)cols + eps);
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const float gg[8] = {g[j][0].x, g[j][0].y, g[j][0].z, g[j][0].w, g[j][1].x, g[j][1].y, g[j][1].z, g[j][1].w};

@@ -147,6 +147,30 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* red)
     return r;
 }
 
+// ns_rows::block_sum_pieces over all NS_TAIL_THREADS threads: the pieces of the warps outside the active range are zero, and
+// adding zero is exact, so the value is the one a CTA of `active` threads gets.
+template <int VPT>
+__device__ __forceinline__ float block_sum_pieces(const float (&part)[VPT], int active, float* red)
+{
+    const int warps = active >> 5, warp = threadIdx.x >> 5;
+    float t[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        float v = part[j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        t[j] = v;
+    }
+    if ((threadIdx.x & 31) == 0 && warp < warps) {
+#pragma unroll
+        for (int j = 0; j < VPT; j++) red[j * warps + warp] = t[j];
+    }
+    __syncthreads();
+    float r = red[0];
+    for (int w = 1; w < VPT * warps; w++) r += red[w];
+    return r;
+}
+
 template <int VPT>
 __device__ __forceinline__ void quantize_row(const float (&x)[VPT * 8], bool on, int active, int8_t* __restrict__ q_row, float* __restrict__ scale_out,
                                              float* red)
@@ -184,18 +208,27 @@ __device__ __forceinline__ void layernorm_quantize_row(float (&x)[VPT * 8], bool
             b[j][0] = __ldg(reinterpret_cast<const float4*>(beta + col)); b[j][1] = __ldg(reinterpret_cast<const float4*>(beta + col + 4));
         }
     }
-    float s = 0.0f;
-    if (on) {
+    float part[VPT];
 #pragma unroll
-        for (int i = 0; i < VPT * 8; i++) s += x[i];
-    }
-    const float mean = block_reduce(s, false, sh.red[0]) / (float)cols;
-    float v2 = 0.0f;
-    if (on) {
+    for (int j = 0; j < VPT; j++) {
+        float s = 0.0f;
+        if (on) {
 #pragma unroll
-        for (int i = 0; i < VPT * 8; i++) { const float d = x[i] - mean; v2 = fmaf(d, d, v2); }
+            for (int i = 0; i < 8; i++) s += x[j * 8 + i];
+        }
+        part[j] = s;
     }
-    const float inv = 1.0f / sqrtf(block_reduce(v2, false, sh.red[1]) / (float)cols + eps);
+    const float mean = block_sum_pieces<VPT>(part, active, sh.red[0]) / (float)cols;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        float v2 = 0.0f;
+        if (on) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) { const float d = x[j * 8 + i] - mean; v2 = fmaf(d, d, v2); }
+        }
+        part[j] = v2;
+    }
+    const float inv = 1.0f / sqrtf(block_sum_pieces<VPT>(part, active, sh.red[1]) / (float)cols + eps);
     if (on) {
 #pragma unroll
         for (int j = 0; j < VPT; j++) {
