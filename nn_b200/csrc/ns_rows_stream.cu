@@ -169,11 +169,9 @@ __global__ void __launch_bounds__(RS_THREADS) ns_rows_stream_kernel(const uint16
             }
             return t;
         };
-        // A SUM over the row in the order of the few-row kernels (ns_rows::block_reduce with one vector per thread): vector by
-        // vector (its eight elements left to right, done by the caller), the 32 vectors of a piece by the xor-shuffle tree, the
-        // pieces one after the other -- so LayerNorm gives the same bits whichever kernel family a pass takes (rows of up to
-        // 2048 columns, where the few-row kernels hold one vector per thread).  part[k] is this lane's vector of piece
-        // sub * VEC + k.
+        // A SUM over the row in the order of ns_rows::block_sum_pieces: vector by vector (its eight elements left to right, done
+        // by the caller), the 32 vectors of a piece by the xor-shuffle tree, the pieces one after the other -- so LayerNorm
+        // gives the same bits whichever kernel family a pass takes.  part[k] is this lane's vector of piece sub * VEC + k.
         auto group_sum = [&](const float (&part)[VEC], int which, bool first_of_row, bool* all_ok) {
             float t[VEC];
 #pragma unroll
